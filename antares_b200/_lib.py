@@ -1,0 +1,72 @@
+"""ctypes binding of libantares_b200.so (the C ABI declared in include/antares_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libantares_b200.so")
+
+OK, EINVAL, ECUDA, EUNSUPPORTED, ETIMEOUT = 0, 1, 2, 3, 4
+F16, F32 = 0, 1
+
+
+class Ab200Error(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("antares_b200 error %d: %s" % (code, text))
+        self.code = code
+
+
+_vp, _i, _l, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_size_t
+
+# name -> argument types; every function returns int except the two noted below.
+SIGNATURES = {
+    "ab200_device_info": [_i, _vp],
+    "ab200_w4_unpack": [_vp, _i, _i, _vp, _vp],
+    "ab200_w4_pack": [_vp, _i, _i, _vp, _vp],
+    "ab200_w4_dequant": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ab200_w4a16_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ab200_w4a16_gemv_residual": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ab200_w4a16_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],
+    "ab200_rmsnorm_vsum": [_vp, _vp, _vp, _vp, _sz, _f, _f, _i, _vp],
+    "ab200_rmsnorm": [_vp, _i, _vp, _vp, _i, _i, _f, _vp],
+    "ab200_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "ab200_softmax": [_vp, _vp, _i, _i, _i, _vp],
+    "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _f, _vp],
+    "ab200_embed_lookup": [_vp, _vp, _vp, _i, _i, _vp],
+    "ab200_rope_kv_store": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _vp],
+    "ab200_silu_mul": [_vp, _vp, _i, _vp],
+    "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
+    "ab200_greedy_next": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp],
+}
+OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version"]
+
+_lib = None
+
+
+def load():
+    """Loads the library (once).  Raises ImportError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s not found: run `python -m antares_b200.build` (needs nvcc); "
+                              "antares_b200 has no CPU or eager fallback" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_int
+        L.ab200_last_error.restype = ctypes.c_char_p
+        L.ab200_last_error.argtypes = []
+        L.ab200_abi_version.restype = ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def call(name, *args):
+    L = load()
+    rc = getattr(L, name)(*args)
+    if rc != OK:
+        raise Ab200Error(rc, L.ab200_last_error().decode())

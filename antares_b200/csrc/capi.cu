@@ -1,0 +1,52 @@
+// Error reporting and device probe of the antares_b200 C ABI.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace ab200 {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void clear_error() { g_err[0] = 0; }
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" const char *ab200_last_error(void) { return g_err; }
+extern "C" int ab200_abi_version(void) { return 1; }
+
+extern "C" int ab200_device_info(int device, int *out8_host) {
+  clear_error();
+  AB200_REQUIRE(out8_host != nullptr, "device_info: null output");
+  const cudaDeviceAttr attrs[8] = {cudaDevAttrMultiProcessorCount, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                   cudaDevAttrL2CacheSize, cudaDevAttrClockRate, cudaDevAttrMemoryClockRate,
+                                   cudaDevAttrGlobalMemoryBusWidth, cudaDevAttrComputeCapabilityMajor,
+                                   cudaDevAttrMaxThreadsPerBlock};
+  for (int i = 0; i < 8; ++i) AB200_CUDA(cudaDeviceGetAttribute(&out8_host[i], attrs[i], device));
+  int minor = 0;
+  AB200_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
+  out8_host[6] = out8_host[6] * 10 + minor;
+  return AB200_OK;
+}

@@ -1,0 +1,75 @@
+// Shared helpers for the antares_b200 kernel library (sm_100a only).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/antares_b200.h"
+
+namespace ab200 {
+
+// Records the calling thread's last error text; returns `code` so call sites can `return fail(...)`.
+int fail(int code, const char *fmt, ...);
+void clear_error();
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Checks the launch itself (not completion: nothing here synchronises).
+#define AB200_CHECK_LAUNCH(what)                                                        \
+  do {                                                                                  \
+    cudaError_t e__ = cudaGetLastError();                                               \
+    if (e__ != cudaSuccess) return ::ab200::fail(AB200_ECUDA, "%s: %s", what, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define AB200_CUDA(call)                                                                \
+  do {                                                                                  \
+    cudaError_t e__ = (call);                                                           \
+    if (e__ != cudaSuccess) return ::ab200::fail(AB200_ECUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define AB200_REQUIRE(cond, ...)                                                        \
+  do {                                                                                  \
+    if (!(cond)) return ::ab200::fail(AB200_EINVAL, __VA_ARGS__);                       \
+  } while (0)
+
+int sm_count();  // SMs of the current device (cached per device)
+
+// ---- device helpers ---------------------------------------------------------------------
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint2 ldg_nc_v2(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+template <int IMM>
+__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(r) : "r"(a), "r"(b), "r"(c), "n"(IMM));
+  return r;
+}
+
+__device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace ab200

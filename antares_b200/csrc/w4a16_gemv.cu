@@ -1,0 +1,391 @@
+// W4A16 decode GEMV for sm_100a: out[M,N] = x[M,K] . dequant(qweight[K/8,N], scales[K/group,N]).
+//
+// Replaces the kernel the reference generates from samples/05_llama2_7b_int4.py:135-139.
+//
+// Data layout in HBM (unchanged from the reference: no repacking is needed to stream it):
+//   qweight int32 [K/8, N], N contiguous: one 16-byte load = 4 columns x 8 k-values; a warp
+//   reads 512 contiguous bytes of one packed row (128 columns).
+//   scales fp16/fp32 [K/group, N]; x [M, K]; out [M, N].
+//
+// Decomposition: CTA = 128 columns x a contiguous slice of K; its 8 warps take 32-k "units"
+// (4 packed rows) round-robin, with the next unit's 4 loads in flight while the current one is
+// multiplied.  The K slices of one column tile are the CTAs of one thread-block cluster; the
+// partial sums meet in distributed shared memory in a fixed order (deterministic, no global
+// scratch, no atomics).  HBM-bound: algorithmic bytes = K*N/2 + (K/group)*N*2 + M*K*2 + M*N*2.
+//
+// fp16 path arithmetic: nibbles become fp16 (q-8) exactly (0x6400 magic + one HSUB2/HFMA2),
+// 16 products per column lane are chained in HFMA2, then widened to fp32 and multiplied by the
+// group scale; everything across units, warps and CTAs is fp32.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ab200 {
+
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int TILE_N = 128;  // 32 lanes x 4 columns
+constexpr int UNIT_ROWS = 4; // packed rows per unit
+constexpr int UNIT_K = UNIT_ROWS * 8;
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1 };
+
+struct GemvParams {
+  const void *x;
+  const int32_t *qw;
+  const void *scales;
+  void *out;
+  int K, N, group;
+  int units;  // K / 32
+};
+
+// (q-8) for the eight nibbles of `w` as four half2: (n0,n4) (n1,n5) (n2,n6) (n3,n7).
+__device__ __forceinline__ void unpack8(uint32_t w, __half2 (&v)[4]) {
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;  // 1024.0 | bits
+  const __half2 c1032 = __half2half2(__ushort_as_half(0x6408));  // 1032
+  const __half2 c16th = __half2half2(__ushort_as_half(0x2C00));  // 1/16
+  const __half2 cm72 = __half2half2(__ushort_as_half(0xD480));   // -72
+  uint32_t w8 = w >> 8;
+  uint32_t t0 = lop3<0xEA>(w, LO, MAGIC);   // (a & b) | c
+  uint32_t t1 = lop3<0xEA>(w, HI, MAGIC);   // 1024 + 16 q
+  uint32_t t2 = lop3<0xEA>(w8, LO, MAGIC);
+  uint32_t t3 = lop3<0xEA>(w8, HI, MAGIC);
+  v[0] = __hsub2(u2h2(t0), c1032);
+  v[1] = __hfma2(u2h2(t1), c16th, cm72);
+  v[2] = __hsub2(u2h2(t2), c1032);
+  v[3] = __hfma2(u2h2(t3), c16th, cm72);
+}
+
+// Cross-warp, then cross-CTA (cluster) reduction of per-thread partials and the epilogue.
+// red: [WARPS][M][128] floats, part: [M][128] floats, both in this CTA's shared memory.
+template <int M, int EPI, typename OutT>
+__device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red, float *part,
+                                                 OutT *out, int N, int tile_n0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+    *reinterpret_cast<float4 *>(&red[(warp * M + m) * TILE_N + lane * 4]) =
+        make_float4(facc[m][0], facc[m][1], facc[m][2], facc[m][3]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < M * TILE_N; i += GEMV_THREADS) {
+    const int m = i / TILE_N, c = i % TILE_N;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) s += red[(w * M + m) * TILE_N + c];
+    part[i] = s;
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned cs = cluster.num_blocks();
+  if (cs > 1) cluster.sync(); else __syncthreads();
+  const unsigned rank = cluster.block_rank();
+  const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
+  for (int i = threadIdx.x; i < M * cols_per; i += GEMV_THREADS) {
+    const int m = i / cols_per, c = rank * cols_per + i % cols_per;
+    float s = 0.f;
+    for (unsigned r = 0; r < cs; ++r) {
+      const float *remote = (cs > 1) ? cluster.map_shared_rank(part, r) : part;
+      s += remote[m * TILE_N + c];
+    }
+    const int n = tile_n0 + c;
+    if (n < N) {
+      if (EPI == EPI_STORE) {
+        if (sizeof(OutT) == 2) reinterpret_cast<__half *>(out)[(size_t)m * N + n] = __float2half_rn(s);
+        else reinterpret_cast<float *>(out)[(size_t)m * N + n] = s;
+      } else {
+        float *o = reinterpret_cast<float *>(out) + (size_t)m * N + n;
+        *o += __half2float(__float2half_rn(s));
+      }
+    }
+  }
+  if (cs > 1) cluster.sync();  // keep `part` alive until every peer has read it
+}
+
+template <int M, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned cs = cluster.num_blocks(), krank = cluster.block_rank();
+  const int tile = blockIdx.x / cs;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = tile * TILE_N + lane * 4;
+  const bool col_ok = n0 < p.N;
+
+  const int u_begin = (int)((long)p.units * krank / cs), u_end = (int)((long)p.units * (krank + 1) / cs);
+  const int k_begin = u_begin * UNIT_K, kslice = (u_end - u_begin) * UNIT_K;
+  const int xs_stride = kslice;  // halves per batch row
+
+  __half *xs = reinterpret_cast<__half *>(smem_raw);
+  float *red = reinterpret_cast<float *>(smem_raw + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));
+  float *part = red + GEMV_WARPS * M * TILE_N;
+
+  const int32_t *qcol = p.qw + n0;
+  const __half *scol = reinterpret_cast<const __half *>(p.scales) + n0;
+
+  uint4 wbuf[2][UNIT_ROWS];
+  uint2 sbuf[2];
+  auto load_unit = [&](int u, int b) {
+    if (col_ok) {
+      const int32_t *q = qcol + (size_t)u * UNIT_ROWS * p.N;
+#pragma unroll
+      for (int r = 0; r < UNIT_ROWS; ++r) wbuf[b][r] = ldg_stream_v4(q + (size_t)r * p.N);
+      sbuf[b] = ldg_nc_v2(scol + (size_t)((u * UNIT_K) / p.group) * p.N);
+    } else {
+#pragma unroll
+      for (int r = 0; r < UNIT_ROWS; ++r) wbuf[b][r] = make_uint4(0, 0, 0, 0);
+      sbuf[b] = make_uint2(0, 0);
+    }
+  };
+
+  int u = u_begin + warp;
+  if (u < u_end) load_unit(u, 0);  // weights are on their way before x is staged
+
+  // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
+  // (x0,x4)(x1,x5)(x2,x6)(x3,x7): the pairing the nibble unpack produces.
+  {
+    const __half *xg = reinterpret_cast<const __half *>(p.x);
+    const int rows = kslice / 8;
+    for (int i = threadIdx.x; i < M * rows; i += GEMV_THREADS) {
+      const int m = i / rows, r = i % rows;
+      uint4 v = *reinterpret_cast<const uint4 *>(xg + (size_t)m * p.K + k_begin + r * 8);
+      uint4 o;
+      o.x = __byte_perm(v.x, v.z, 0x5410);
+      o.y = __byte_perm(v.x, v.z, 0x7632);
+      o.z = __byte_perm(v.y, v.w, 0x5410);
+      o.w = __byte_perm(v.y, v.w, 0x7632);
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = o;
+    }
+  }
+  __syncthreads();
+
+  float facc[M][4];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) facc[m][c] = 0.f;
+
+  auto compute_unit = [&](int uu, int b) {
+    __half2 hacc[M][4];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) hacc[m][c] = __half2half2(__ushort_as_half(0));
+    const __half *xu = xs + (uu - u_begin) * UNIT_K;
+#pragma unroll
+    for (int r = 0; r < UNIT_ROWS; ++r) {
+      uint4 xr[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) xr[m] = *reinterpret_cast<const uint4 *>(xu + (size_t)m * xs_stride + r * 8);
+      const uint32_t wr[4] = {wbuf[b][r].x, wbuf[b][r].y, wbuf[b][r].z, wbuf[b][r].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        __half2 v[4];
+        unpack8(wr[c], v);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          hacc[m][c] = __hfma2(v[0], u2h2(xr[m].x), hacc[m][c]);
+          hacc[m][c] = __hfma2(v[1], u2h2(xr[m].y), hacc[m][c]);
+          hacc[m][c] = __hfma2(v[2], u2h2(xr[m].z), hacc[m][c]);
+          hacc[m][c] = __hfma2(v[3], u2h2(xr[m].w), hacc[m][c]);
+        }
+      }
+    }
+    const float2 s01 = __half22float2(u2h2(sbuf[b].x)), s23 = __half22float2(u2h2(sbuf[b].y));
+    const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 f = __half22float2(hacc[m][c]);
+        facc[m][c] = fmaf(sc[c], f.x + f.y, facc[m][c]);
+      }
+  };
+
+  // Two-deep software pipeline over this warp's units.
+  while (u < u_end) {
+    const int u1 = u + GEMV_WARPS;
+    if (u1 < u_end) load_unit(u1, 1);
+    compute_unit(u, 0);
+    if (u1 >= u_end) break;
+    const int u2 = u1 + GEMV_WARPS;
+    if (u2 < u_end) load_unit(u2, 0);
+    compute_unit(u1, 1);
+    u = u2;
+  }
+
+  if (EPI == EPI_STORE)
+    reduce_and_store<M, EPI, __half>(facc, red, part, reinterpret_cast<__half *>(p.out), p.N, tile * TILE_N);
+  else
+    reduce_and_store<M, EPI, float>(facc, red, part, reinterpret_cast<float *>(p.out), p.N, tile * TILE_N);
+}
+
+// fp32 activations / scales / result: the dtypes the in-tree sample declares
+// (samples/05_llama2_7b_int4.py:75,133,139).  w = scale * (q - 8) is one fp32 multiply, as in
+// IR statement 2; products accumulate in fp32.
+template <int M>
+__global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned cs = cluster.num_blocks(), krank = cluster.block_rank();
+  const int tile = blockIdx.x / cs;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = tile * TILE_N + lane * 4;
+  const bool col_ok = n0 < p.N;
+  const int u_begin = (int)((long)p.units * krank / cs), u_end = (int)((long)p.units * (krank + 1) / cs);
+  const int k_begin = u_begin * UNIT_K, kslice = (u_end - u_begin) * UNIT_K;
+
+  float *xs = reinterpret_cast<float *>(smem_raw);
+  float *red = xs + (size_t)M * kslice;
+  float *part = red + GEMV_WARPS * M * TILE_N;
+
+  const float *xg = reinterpret_cast<const float *>(p.x);
+  for (int i = threadIdx.x; i < M * (kslice / 4); i += GEMV_THREADS) {
+    const int m = i / (kslice / 4), r = i % (kslice / 4);
+    *reinterpret_cast<float4 *>(xs + (size_t)m * kslice + r * 4) =
+        *reinterpret_cast<const float4 *>(xg + (size_t)m * p.K + k_begin + r * 4);
+  }
+  __syncthreads();
+
+  float facc[M][4];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) facc[m][c] = 0.f;
+
+  const int32_t *qcol = p.qw + n0;
+  const float *scol = reinterpret_cast<const float *>(p.scales) + n0;
+  for (int u = u_begin + warp; u < u_end && col_ok; u += GEMV_WARPS) {
+    uint4 wv[UNIT_ROWS];
+    const int32_t *q = qcol + (size_t)u * UNIT_ROWS * p.N;
+#pragma unroll
+    for (int r = 0; r < UNIT_ROWS; ++r) wv[r] = ldg_stream_v4(q + (size_t)r * p.N);
+    const float4 s4 = *reinterpret_cast<const float4 *>(scol + (size_t)((u * UNIT_K) / p.group) * p.N);
+    const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+    const float *xu = xs + (u - u_begin) * UNIT_K;
+#pragma unroll
+    for (int r = 0; r < UNIT_ROWS; ++r) {
+      const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float xv[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) xv[m] = xu[(size_t)m * kslice + r * 8 + j];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          // 2^23 + q as a float, minus (2^23 + 8): q - 8 exactly.
+          const float qm8 = __uint_as_float(0x4B000000u | ((wr[c] >> (4 * j)) & 15u)) - 8388616.0f;
+          const float w = sc[c] * qm8;
+#pragma unroll
+          for (int m = 0; m < M; ++m) facc[m][c] = fmaf(xv[m], w, facc[m][c]);
+        }
+      }
+    }
+  }
+  reduce_and_store<M, EPI_STORE, float>(facc, red, part, reinterpret_cast<float *>(p.out), p.N, tile * TILE_N);
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+static int pick_cluster(int tiles, int units) {
+  const int target = 2 * sm_count();
+  int cs = 1;
+  while (cs < 8 && tiles * cs < target && units / (cs * 2) >= GEMV_WARPS) cs *= 2;
+  return cs;
+}
+
+template <typename Kern>
+static int launch_gemv(Kern kern, const GemvParams &p, int M, int elt, cudaStream_t stream) {
+  const int tiles = (p.N + TILE_N - 1) / TILE_N;
+  const int cs = pick_cluster(tiles, p.units);
+  const int kslice_max = ((p.units + cs - 1) / cs) * UNIT_K;
+  size_t smem = (((size_t)M * kslice_max * elt + 15) & ~(size_t)15) +
+                (size_t)(GEMV_WARPS + 1) * M * TILE_N * sizeof(float);
+  if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: K slice of %d values x M=%d does not fit shared memory", kslice_max, M);
+  if (smem > 48 * 1024) {
+    // Raising the limit is idempotent and cheap; doing it per launch keeps the library stateless
+    // across devices.
+    AB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * cs, 1, 1);
+  cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  AB200_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+  return AB200_OK;
+}
+
+static int check_gemv_args(const void *x, const int32_t *qw, const void *scales, const void *out, int M,
+                           int K, int N, int group) {
+  AB200_REQUIRE(x && qw && scales && out, "w4a16_gemv: null pointer");
+  AB200_REQUIRE(M >= 1 && M <= 16, "w4a16_gemv: M=%d outside 1..16 (use ab200_w4a16_gemm for prefill)", M);
+  AB200_REQUIRE(K > 0 && K % UNIT_K == 0, "w4a16_gemv: K=%d must be a positive multiple of 32", K);
+  AB200_REQUIRE(group > 0 && group % UNIT_K == 0 && K % group == 0, "w4a16_gemv: group=%d must be a multiple of 32 dividing K=%d", group, K);
+  AB200_REQUIRE(N > 0 && N % 4 == 0, "w4a16_gemv: N=%d must be a positive multiple of 4", N);
+  AB200_REQUIRE(aligned16(x) && aligned16(qw) && aligned16(scales) && aligned16(out), "w4a16_gemv: pointers must be 16-byte aligned");
+  return AB200_OK;
+}
+
+template <int EPI>
+static int gemv_f16_dispatch(GemvParams p, int M, cudaStream_t s) {
+  // Batches above 4 re-stream the weights per group of 4 rows.
+  const size_t out_elt = (EPI == EPI_STORE) ? sizeof(__half) : sizeof(float);
+  for (int m0 = 0; m0 < M; m0 += 4) {
+    const int mc = (M - m0 < 4) ? (M - m0) : 4;
+    GemvParams q = p;
+    q.x = reinterpret_cast<const __half *>(p.x) + (size_t)m0 * p.K;
+    q.out = reinterpret_cast<char *>(p.out) + (size_t)m0 * p.N * out_elt;
+    int rc;
+    switch (mc) {
+      case 1: rc = launch_gemv(w4a16_gemv_f16_kernel<1, EPI>, q, 1, 2, s); break;
+      case 2: rc = launch_gemv(w4a16_gemv_f16_kernel<2, EPI>, q, 2, 2, s); break;
+      case 3: rc = launch_gemv(w4a16_gemv_f16_kernel<3, EPI>, q, 3, 2, s); break;
+      default: rc = launch_gemv(w4a16_gemv_f16_kernel<4, EPI>, q, 4, 2, s); break;
+    }
+    if (rc) return rc;
+  }
+  return AB200_OK;
+}
+
+static int gemv_f32_dispatch(GemvParams p, int M, cudaStream_t s) {
+  for (int m0 = 0; m0 < M; m0 += 2) {
+    const int mc = (M - m0 < 2) ? (M - m0) : 2;
+    GemvParams q = p;
+    q.x = reinterpret_cast<const float *>(p.x) + (size_t)m0 * p.K;
+    q.out = reinterpret_cast<float *>(p.out) + (size_t)m0 * p.N;
+    int rc = (mc == 1) ? launch_gemv(w4a16_gemv_f32_kernel<1>, q, 1, 4, s)
+                       : launch_gemv(w4a16_gemv_f32_kernel<2>, q, 2, 4, s);
+    if (rc) return rc;
+  }
+  return AB200_OK;
+}
+
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const void *scales, void *out,
+                                int M, int K, int N, int group, int dtype, void *stream) {
+  clear_error();
+  if (int rc = check_gemv_args(x, qweight, scales, out, M, K, N, group)) return rc;
+  GemvParams p{x, qweight, scales, out, K, N, group, K / UNIT_K};
+  if (dtype == AB200_F16) return gemv_f16_dispatch<EPI_STORE>(p, M, (cudaStream_t)stream);
+  if (dtype == AB200_F32) return gemv_f32_dispatch(p, M, (cudaStream_t)stream);
+  return fail(AB200_EINVAL, "w4a16_gemv: unknown dtype %d", dtype);
+}
+
+extern "C" int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, const void *scales,
+                                         float *resid_f32, int M, int K, int N, int group, void *stream) {
+  clear_error();
+  if (int rc = check_gemv_args(x, qweight, scales, resid_f32, M, K, N, group)) return rc;
+  GemvParams p{x, qweight, scales, resid_f32, K, N, group, K / UNIT_K};
+  return gemv_f16_dispatch<EPI_RESIDUAL>(p, M, (cudaStream_t)stream);
+}

@@ -1,0 +1,178 @@
+"""torch-tensor front ends of the C ABI.  Tensors must live on a CUDA device; launches go to
+torch's current stream (the reference launches on the NULL stream, frameworks/pytorch/main_ops.cc:44).
+Nothing here computes on the CPU: a CPU tensor is an error, not a fallback.
+"""
+import torch
+
+from . import _lib
+from ._lib import F16, F32, call
+
+_DT = {torch.float16: F16, torch.float32: F32}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t, name, dtype=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (antares_b200 has no CPU path)" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError("%s must be %s, got %s" % (name, dtype, t.dtype))
+    return t.data_ptr()
+
+
+def _code(dtype):
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise ValueError("dtype %s is outside the built kernel family (float16, float32)" % dtype)
+
+
+def device_info(device=0):
+    import ctypes
+    buf = (ctypes.c_int * 8)()
+    call("ab200_device_info", int(device), ctypes.cast(buf, ctypes.c_void_p))
+    keys = ["sm_count", "smem_optin_bytes", "l2_bytes", "sm_clock_khz", "mem_clock_khz", "bus_width_bits", "cc", "max_threads"]
+    return dict(zip(keys, list(buf)))
+
+
+def w4_unpack(qweight):
+    Kp, N = qweight.shape
+    out = torch.empty((Kp * 8, N), dtype=torch.uint8, device=qweight.device)
+    call("ab200_w4_unpack", _chk(qweight, "qweight", torch.int32), Kp * 8, N, out.data_ptr(), _stream())
+    return out
+
+
+def w4_pack(q):
+    K, N = q.shape
+    out = torch.empty((K // 8, N), dtype=torch.int32, device=q.device)
+    call("ab200_w4_pack", _chk(q, "q", torch.uint8), K, N, out.data_ptr(), _stream())
+    return out
+
+
+def w4_dequant(qweight, scales, group=128):
+    Kp, N = qweight.shape
+    out = torch.empty((Kp * 8, N), dtype=scales.dtype, device=qweight.device)
+    call("ab200_w4_dequant", _chk(qweight, "qweight", torch.int32), _chk(scales, "scales"), Kp * 8, N, group,
+         _code(scales.dtype), out.data_ptr(), _stream())
+    return out
+
+
+def _gemm_shapes(x, qweight, scales, group):
+    Kp, N = qweight.shape
+    K = Kp * 8
+    if x.shape[-1] != K:
+        raise ValueError("x has %d features but qweight packs %d" % (x.shape[-1], K))
+    M = x.numel() // K
+    if group is None:
+        group = K // scales.shape[0]
+    if scales.shape != (K // group, N):
+        raise ValueError("scales shape %s does not match [K/group=%d, N=%d]" % (tuple(scales.shape), K // group, N))
+    if scales.dtype != x.dtype:
+        raise ValueError("x (%s) and scales (%s) must share a dtype" % (x.dtype, scales.dtype))
+    return M, K, N, group
+
+
+def w4a16_gemv(x, qweight, scales, out=None, group=None):
+    """out[..., N] = x[..., K] . dequant(qweight, scales); M = x.numel()/K <= 16."""
+    M, K, N, group = _gemm_shapes(x, qweight, scales, group)
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=x.dtype, device=x.device)
+    elif out.numel() != M * N or out.dtype != x.dtype:
+        raise ValueError("out must hold %d elements of %s" % (M * N, x.dtype))
+    call("ab200_w4a16_gemv", _chk(x, "x"), _chk(qweight, "qweight", torch.int32), _chk(scales, "scales"),
+         _chk(out, "out"), M, K, N, group, _code(x.dtype), _stream())
+    return out
+
+
+def w4a16_gemv_residual(x, qweight, scales, resid, group=None):
+    """resid_f32[..., N] += fp16_round(x . W)."""
+    M, K, N, group = _gemm_shapes(x, qweight, scales, group)
+    if resid.numel() != M * N:
+        raise ValueError("resid must hold %d elements" % (M * N))
+    call("ab200_w4a16_gemv_residual", _chk(x, "x", torch.float16), _chk(qweight, "qweight", torch.int32),
+         _chk(scales, "scales", torch.float16), _chk(resid, "resid", torch.float32), M, K, N, group, _stream())
+    return resid
+
+
+def w4a16_gemm(x, qweight, scales, out=None, group=None):
+    """Prefill contraction on tensor cores; x [M, K] with M a multiple of 128."""
+    Kp, N = qweight.shape
+    K = Kp * 8
+    M = x.numel() // K
+    if group is None:
+        group = K // scales.shape[0]
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=x.dtype, device=x.device)
+    call("ab200_w4a16_gemm", _chk(x, "x"), _chk(qweight, "qweight", torch.int32), _chk(scales, "scales"),
+         _chk(out, "out"), M, K, N, group, _code(x.dtype), _stream())
+    return out
+
+
+def w4a16_matmul(x, qweight, scales, out=None, group=None):
+    """The exported op of samples/05_llama2_7b_int4.py:135-144 for any batch: decode kernel up to
+    16 rows, tensor-core kernel above."""
+    M = x.numel() // (qweight.shape[0] * 8)
+    if M <= 16:
+        return w4a16_gemv(x, qweight, scales, out, group)
+    return w4a16_gemm(x, qweight, scales, out, group)
+
+
+def sigmoid(x, out=None):
+    if out is None:
+        out = torch.empty_like(x)
+    call("ab200_sigmoid", _chk(x, "x"), _chk(out, "out", x.dtype), x.numel(), _code(x.dtype), _stream())
+    return out
+
+
+def rmsnorm_vsum(x, vsum, weight, inv_n, eps=1e-6, out=None):
+    if out is None:
+        out = torch.empty_like(x)
+    call("ab200_rmsnorm_vsum", _chk(x, "x"), _chk(vsum, "vsum", torch.float32), _chk(weight, "weight", x.dtype),
+         _chk(out, "out", x.dtype), x.numel(), float(inv_n), float(eps), _code(x.dtype), _stream())
+    return out
+
+
+def rmsnorm(x, weight, eps=1e-6, out=None):
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    call("ab200_rmsnorm", _chk(x, "x"), _code(x.dtype), _chk(weight, "weight", torch.float16),
+         _chk(out, "out", torch.float16), rows, cols, float(eps), _stream())
+    return out
+
+
+def rope(x, pos, inv_freq, out=None):
+    rows, H, D = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    call("ab200_rope", _chk(x, "x", torch.float16), _chk(inv_freq, "inv_freq", torch.float32),
+         _chk(pos, "pos", torch.int32), _chk(out, "out", torch.float16), rows, H, D, _stream())
+    return out
+
+
+def softmax(x, out=None):
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if out is None:
+        out = torch.empty_like(x)
+    call("ab200_softmax", _chk(x, "x"), _chk(out, "out", x.dtype), rows, cols, _code(x.dtype), _stream())
+    return out
+
+
+def attention_decode(q, k_cache, v_cache, seq_len_dev, scale, out=None, kv_stride=None, max_seq=None):
+    H, D = q.shape
+    if kv_stride is None:
+        kv_stride = k_cache.stride(0)
+    if max_seq is None:
+        max_seq = k_cache.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    call("ab200_attention_decode", _chk(q, "q", torch.float16), k_cache.data_ptr(), v_cache.data_ptr(),
+         _chk(out, "out", torch.float16), _chk(seq_len_dev, "seq_len_dev", torch.int32), int(max_seq), H, D,
+         int(kv_stride), float(scale), _stream())
+    return out

@@ -1,0 +1,151 @@
+/*
+ * antares_b200 — C ABI of the B200 (sm_100a) kernel library that stands in for what the
+ * Antares/AutoRT CUDA backend would generate for the Llama-2-7B int4 operator path.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in `_host`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - fp16 tensors are IEEE binary16; `dtype` is AB200_F16 or AB200_F32 and names the dtype
+ *     of activations, scales and results together (the reference declares them together,
+ *     samples/05_llama2_7b_int4.py:133,139);
+ *   - functions return AB200_OK (0) or an error code; ab200_last_error() gives the text.
+ *     Nothing calls exit() (the reference's CHECK_OK does, graph_evaluator/execute_module.hpp:40);
+ *   - no function allocates device memory or synchronises the device unless it says so;
+ *     all are legal inside CUDA stream capture unless they say otherwise.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to the
+ * reference project root).
+ */
+#ifndef ANTARES_B200_H_
+#define ANTARES_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  AB200_OK = 0,
+  AB200_EINVAL = 1,       /* bad shape / alignment / null pointer */
+  AB200_ECUDA = 2,        /* a CUDA runtime call failed */
+  AB200_EUNSUPPORTED = 3, /* valid request outside the built kernel family */
+  AB200_ETIMEOUT = 4      /* a bounded device-side wait ran out */
+};
+
+enum { AB200_F16 = 0, AB200_F32 = 1 };
+
+/* Text of the last error on the calling thread ("" if none). */
+const char *ab200_last_error(void);
+int ab200_abi_version(void);
+
+/* Device property probe; replaces engine/cuda_properties.cc:35-52 (which prints
+ * key/value pairs for the code generator).  Fills 8 ints:
+ * [0] SM count, [1] max shared memory per block (opt-in, bytes), [2] L2 bytes,
+ * [3] SM clock kHz, [4] memory clock kHz, [5] memory bus width bits,
+ * [6] compute capability major*10+minor, [7] max threads per block.
+ * Host call; touches no stream. */
+int ab200_device_info(int device, int *out8_host);
+
+/* ---- int4 packing ------------------------------------------------------------------------
+ * Layout (GPTQ, as loaded by samples/05_llama2_7b_int4.py:24-28): qweight int32 [K/8, N],
+ * N contiguous; word (r, n) holds the eight 4-bit values of rows 8r..8r+7 of column n,
+ * lowest nibble = lowest row. */
+
+/* q_out u8 [K, N] = (qweight[S/8, N] >> (S%8*4)) & 15  — IR statement 1,
+ * samples/05_llama2_7b_int4.py:136. */
+int ab200_w4_unpack(const int32_t *qweight, int K, int N, uint8_t *q_out, void *stream);
+
+/* Inverse of ab200_w4_unpack (no reference counterpart: the sample loads packed weights). */
+int ab200_w4_pack(const uint8_t *q, int K, int N, int32_t *qweight_out, void *stream);
+
+/* w_out [K, N] = scales[S/group, N] * (q - 8) in `dtype` — IR statements 1-2,
+ * samples/05_llama2_7b_int4.py:136-137.  Bit-exact with the reference's CPU backend. */
+int ab200_w4_dequant(const int32_t *qweight, const void *scales, int K, int N, int group,
+                     int dtype, void *w_out, void *stream);
+
+/* ---- W4A16 contraction --------------------------------------------------------------------
+ * out[M, N] = sum_S x[M, S] * (scales[S/group, N] * (q[S, N] - 8)), fp32 accumulation —
+ * the exported op `my_custom_fn` of samples/05_llama2_7b_int4.py:135-144 (`matmul_dequat`).
+ * This is the decode path (M <= 16): weights are streamed once from HBM, no tensor cores.
+ * Constraints: K % 32 == 0, group % 32 == 0, K % group == 0, N % 4 == 0, 1 <= M <= 16,
+ * pointers 16-byte aligned. */
+int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const void *scales, void *out, int M,
+                     int K, int N, int group, int dtype, void *stream);
+
+/* Same contraction with the decode step's residual update fused into the epilogue:
+ *   resid_f32[M, N] += fp16_round(out[M, N])        (x, scales fp16)
+ * replaces `xb = matmul_dequat(...); x = x + xb`, samples/05_llama2_7b_int4.py:167-168,172-173. */
+int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, const void *scales,
+                              float *resid_f32, int M, int K, int N, int group, void *stream);
+
+/* Prefill contraction on tensor cores (tcgen05 + TMEM): same arithmetic, M a multiple of 128.
+ * Replaces the same exported op called with a leading M axis. */
+int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const void *scales, void *out, int M,
+                     int K, int N, int group, int dtype, void *stream);
+
+/* ---- elementwise / reduction operators ---------------------------------------------------- */
+
+/* out[i] = 1 - 1 / (1 + exp(x[i])) — README.md:66 (`sigmoid_f32`); dtype F32 or F16. */
+int ab200_sigmoid(const void *x, void *out, size_t n, int dtype, void *stream);
+
+/* autort.ops.rmsnorm_f32(x, vsum, weight, extra=[inv_n]) — call site
+ * samples/05_llama2_7b_int4.py:128-131: out[i] = x[i] * rsqrt(vsum[0]*inv_n + eps) * weight[i]. */
+int ab200_rmsnorm_vsum(const void *x, const float *vsum, const void *weight, void *out, size_t n,
+                       float inv_n, float eps, int dtype, void *stream);
+
+/* Row-wise RMSNorm that computes the sum of squares itself (replaces the torch reduction plus
+ * the op above, samples/05_llama2_7b_int4.py:128-131).  x [rows, cols] in x_dtype (F16 or
+ * F32), weight fp16 [cols], out fp16 [rows, cols]; cols % 8 == 0, cols <= 16384. */
+int ab200_rmsnorm(const void *x, int x_dtype, const void *weight_f16, void *out_f16, int rows,
+                  int cols, float eps, void *stream);
+
+/* autort.ops.rotary_f32(x.view(H,2,D/2), inv_freq[D], out[H,D], extra=[pos]) — call site
+ * samples/05_llama2_7b_int4.py:157-158, batched: x, out fp16 [rows, H, D]; row r is rotated by
+ * position pos[r] (int32 device array); inv_freq fp32 [D/2 or D]. Rotate-half convention. */
+int ab200_rope(const void *x_f16, const float *inv_freq, const int32_t *pos, void *out_f16,
+               int rows, int H, int D, void *stream);
+
+/* Row softmax — AntaresIR.md:226.  x, out [rows, cols] in dtype. */
+int ab200_softmax(const void *x, void *out, int rows, int cols, int dtype, void *stream);
+
+/* autort.ops.attention_f32(q[H,D], K[S,H,D], V[S,H,D], att_f[1]) — call site
+ * samples/05_llama2_7b_int4.py:161-165.  fp16 q/K/V/out, fp32 math.  The number of cache rows
+ * attended is S = *seq_len_dev (a device int, so a captured graph can be replayed as the
+ * sequence grows); kv_stride = elements between consecutive cache rows; D == 128. */
+int ab200_attention_decode(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16,
+                           void *out_f16, const int32_t *seq_len_dev, int max_seq, int H, int D,
+                           long kv_stride, float scale, void *stream);
+
+/* ---- decode-step glue (replaces torch eager ops in samples/05_llama2_7b_int4.py:146-177) -- */
+
+/* x_f32[d] = embed_f16[token, d], token = *token_dev  (line 147). */
+int ab200_embed_lookup(const void *embed_f16, const int32_t *token_dev, float *x_f32, int dim,
+                       int vocab, void *stream);
+
+/* Splits the fused projection output vqk[3*Hl*D] (order V, Q, K as in line 27), rotates Q and
+ * K at position *pos_dev, writes q_out[Hl*D], and stores K and V into cache row *pos_dev
+ * (lines 151-158). */
+int ab200_rope_kv_store(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev,
+                        void *q_out_f16, void *k_cache_f16, void *v_cache_f16, int H, int D,
+                        long kv_stride, int max_seq, void *stream);
+
+/* out[i] = silu(gate_up[i]) * gate_up[n + i], fp32 math (line 171). */
+int ab200_silu_mul(const void *gate_up_f16, void *out_f16, int n, void *stream);
+
+/* logits_f32[N] = W[N, K] . x[K]; W fp16 row-major (line 176: classifier matmul). */
+int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, int K, int N,
+                     void *stream);
+
+/* Greedy sampling and loop bookkeeping on the device (lines 197-207): next = argmax(logits)
+ * (first maximum) unless *pos_dev + 1 < n_prompt, in which case next = prompt[*pos_dev + 1];
+ * writes next to *token_dev and to out_tokens[*pos_dev + 1] (if non-null); *pos_dev += 1.
+ * For tensor-parallel vocab shards use vocab_offset and a later ab200_argmax_merge. */
+int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
+                      int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANTARES_B200_H_ */

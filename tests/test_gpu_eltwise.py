@@ -1,0 +1,98 @@
+"""GPU parity tests of the elementwise / reduction operators (BASELINE config 1 shapes and the
+golden vectors of the reference runtime).  Tolerance: max|err| <= 1e-2 * max|ref|."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from antares_b200 import ops
+from oracle import cport
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _err(y, ref):
+    y, ref = y.astype(np.float32), ref.astype(np.float32)
+    return np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+def test_golden_elementwise(cuda, golden_dir):
+    g = dict(np.load(os.path.join(golden_dir, "softmax_f16_8x256.npz")))
+    assert _err(ops.softmax(_dev(g["x"], cuda)).cpu().numpy(), g["y"]) <= TOL
+    g = dict(np.load(os.path.join(golden_dir, "sigmoid_f32_1000.npz")))
+    assert _err(ops.sigmoid(_dev(g["x"], cuda)).cpu().numpy(), g["y"]) <= 1e-5
+    g = dict(np.load(os.path.join(golden_dir, "rmsnorm_f16_4x512.npz")))
+    assert _err(ops.rmsnorm(_dev(g["x"], cuda), _dev(g["weight"], cuda)).cpu().numpy(), g["y"]) <= TOL
+    g = dict(np.load(os.path.join(golden_dir, "rope_f16_6x4x128.npz")))
+    y = ops.rope(_dev(g["x"], cuda), _dev(g["pos"], cuda), _dev(g["inv_freq"], cuda)).cpu().numpy()
+    assert _err(y, g["y"]) <= TOL
+    g = dict(np.load(os.path.join(golden_dir, "attention_f16_s37_h4.npz")))
+    S, H, D = g["k"].shape
+    y = ops.attention_decode(_dev(g["q"], cuda), _dev(g["k"].reshape(S, H * D), cuda), _dev(g["v"].reshape(S, H * D), cuda),
+                             torch.tensor([S], dtype=torch.int32, device=cuda), float(g["scale"][0])).cpu().numpy()
+    assert _err(y, g["y"]) <= TOL
+
+
+def test_config1_sigmoid(cuda):
+    x = np.random.default_rng(0).standard_normal(4096000).astype(np.float32)
+    y = ops.sigmoid(_dev(x, cuda)).cpu().numpy()
+    assert _err(y, cport.sigmoid(x)) <= 1e-5
+    x10 = torch.arange(0, 10, dtype=torch.float32, device=cuda)  # README.md:64-67: 10 elements into N:4096000
+    assert torch.allclose(ops.sigmoid(x10), torch.sigmoid(x10), atol=1e-6)
+    xh = x[:100003].astype(np.float16)[:100000]
+    assert _err(ops.sigmoid(_dev(xh, cuda)).cpu().numpy(), cport.sigmoid(xh)) <= TOL
+
+
+def test_config1_rmsnorm(cuda):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((2048, 4096)).astype(np.float16)
+    w = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float16)
+    y = ops.rmsnorm(_dev(x, cuda), _dev(w, cuda), eps=1e-6).cpu().numpy()
+    assert _err(y, cport.rmsnorm(x, w, 1e-6)) <= TOL
+    x32 = x[:3].astype(np.float32) * 7
+    assert _err(ops.rmsnorm(_dev(x32, cuda), _dev(w, cuda)).cpu().numpy(), cport.rmsnorm(x32, w)) <= TOL
+    # the AutoRT call form: vsum computed by the caller (samples/05_llama2_7b_int4.py:128-131)
+    v = x32[0]
+    vsum = _dev(np.array([(v * v).sum()], np.float32), cuda)
+    y = ops.rmsnorm_vsum(_dev(v, cuda), vsum, _dev(w.astype(np.float32), cuda), 1.0 / 4096).cpu().numpy()
+    assert _err(y, cport.rmsnorm_vsum_f32(v, np.array([(v * v).sum()], np.float32), w.astype(np.float32), 1.0 / 4096)) <= 1e-5
+
+
+def test_config1_rope(cuda):
+    x = np.random.default_rng(2).standard_normal((2048, 32, 128)).astype(np.float16)
+    pos = np.arange(2048, dtype=np.int32)
+    inv_freq = cport.make_inv_freq(128)
+    y = ops.rope(_dev(x, cuda), _dev(pos, cuda), _dev(inv_freq, cuda)).cpu().numpy()
+    assert _err(y, cport.rope(x, pos, inv_freq)) <= TOL
+    # rotation preserves the norm of each (j, j+D/2) pair
+    n_in = np.hypot(x[..., :64].astype(np.float32), x[..., 64:].astype(np.float32))
+    n_out = np.hypot(y[..., :64].astype(np.float32), y[..., 64:].astype(np.float32))
+    assert np.abs(n_in - n_out).max() <= 1e-2 * n_in.max()
+
+
+def test_config1_softmax(cuda):
+    x = (np.random.default_rng(3).standard_normal((32, 4096)) * 3).astype(np.float16)
+    y = ops.softmax(_dev(x, cuda)).cpu().numpy()
+    assert _err(y, cport.softmax(x)) <= TOL
+    assert np.abs(y.astype(np.float32).sum(-1) - 1).max() < 2e-2
+    x32 = x.astype(np.float32)[:, :1024]
+    assert _err(ops.softmax(_dev(x32, cuda)).cpu().numpy(), cport.softmax(x32)) <= 1e-5
+
+
+@pytest.mark.parametrize("S", [1, 2, 17, 384, 1000])
+def test_attention_decode(cuda, S):
+    rng = np.random.default_rng(S)
+    H, D, max_seq = 32, 128, 1024
+    q = rng.standard_normal((H, D)).astype(np.float16)
+    kc = rng.standard_normal((max_seq, H * D)).astype(np.float16)
+    vc = rng.standard_normal((max_seq, H * D)).astype(np.float16)
+    scale = 1.0 / np.sqrt(D)
+    ref = cport.attention_decode(q, kc, vc, S, scale)
+    y = ops.attention_decode(_dev(q, cuda), _dev(kc, cuda), _dev(vc, cuda), torch.tensor([S], dtype=torch.int32, device=cuda), scale)
+    assert _err(y.cpu().numpy(), ref) <= TOL
