@@ -28,13 +28,17 @@ SIGNATURES = {
     "ab200_w4_dequant": [_vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ab200_w4a16_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_w4a16_gemv_residual": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ab200_w4a16_gemv_f32out": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ab200_residual_add": [_vp, _vp, _i, _vp],
+    "ab200_kernel_status": [_vp],
+    "ab200_set_option": [ctypes.c_char_p, _i],
     "ab200_w4a16_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],
     "ab200_rmsnorm_vsum": [_vp, _vp, _vp, _vp, _sz, _f, _f, _i, _vp],
     "ab200_rmsnorm": [_vp, _i, _vp, _vp, _i, _i, _f, _vp],
     "ab200_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ab200_softmax": [_vp, _vp, _i, _i, _i, _vp],
-    "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _f, _vp],
+    "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],
     "ab200_embed_lookup": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_rope_kv_store": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _vp],
     "ab200_silu_mul": [_vp, _vp, _i, _vp],

@@ -25,14 +25,14 @@ __device__ __forceinline__ void h8_to_f8(const uint4 v, float (&f)[8]) {
 // Phase 2: block-wide max / sum of exp.  Phase 3: 16 row-groups x 16 dim-chunks accumulate P.V.
 __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
                                                                       const __half *__restrict__ vc, __half *__restrict__ out,
-                                                                      const int32_t *__restrict__ seq_len_dev, int max_seq,
-                                                                      long kv_stride, float scale) {
+                                                                      const int32_t *__restrict__ seq_len_dev, int seq_len_add,
+                                                                      int max_seq, long kv_stride, float scale) {
   extern __shared__ __align__(16) float att_smem[];
   float *p = att_smem;                // [max_seq]
   float *red = att_smem + max_seq;    // [16][128]
   __shared__ float sh[32];
   const int h = blockIdx.x;
-  int S = *seq_len_dev;
+  int S = *seq_len_dev + seq_len_add;
   S = S < 0 ? 0 : (S > max_seq ? max_seq : S);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 15, hw = lane >> 4;
@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(DG_THREADS) dense_gemv_kernel(const __half *__
 using namespace ab200;
 
 extern "C" int ab200_attention_decode(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16,
-                                      const int32_t *seq_len_dev, int max_seq, int H, int D, long kv_stride, float scale,
-                                      void *stream) {
+                                      const int32_t *seq_len_dev, int seq_len_add, int max_seq, int H, int D, long kv_stride,
+                                      float scale, void *stream) {
   clear_error();
   AB200_REQUIRE(q_f16 && k_cache_f16 && v_cache_f16 && out_f16 && seq_len_dev, "attention_decode: null pointer");
   AB200_REQUIRE(D == ATT_D, "attention_decode: head size %d is not the built size %d", D, ATT_D);
@@ -153,7 +153,7 @@ extern "C" int ab200_attention_decode(const void *q_f16, const void *k_cache_f16
     AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   attention_decode_kernel<<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const __half *)q_f16, (const __half *)k_cache_f16,
                                                                          (const __half *)v_cache_f16, (__half *)out_f16, seq_len_dev,
-                                                                         max_seq, kv_stride, scale);
+                                                                         seq_len_add, max_seq, kv_stride, scale);
   AB200_CHECK_LAUNCH("attention_decode");
   return AB200_OK;
 }

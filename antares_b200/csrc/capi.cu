@@ -8,6 +8,9 @@ namespace ab200 {
 
 static thread_local char g_err[512] = "";
 
+// Device-side status word: kernels with bounded waits store a site code here when a wait runs out.
+__device__ int g_kernel_error = 0;
+
 int fail(int code, const char *fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -48,5 +51,17 @@ extern "C" int ab200_device_info(int device, int *out8_host) {
   int minor = 0;
   AB200_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device));
   out8_host[6] = out8_host[6] * 10 + minor;
+  return AB200_OK;
+}
+
+extern "C" int ab200_kernel_status(int *status_host) {
+  clear_error();
+  AB200_REQUIRE(status_host != nullptr, "kernel_status: null output");
+  AB200_CUDA(cudaMemcpyFromSymbol(status_host, g_kernel_error, sizeof(int)));
+  if (*status_host != 0) {
+    const int zero = 0;
+    AB200_CUDA(cudaMemcpyToSymbol(g_kernel_error, &zero, sizeof(int)));
+    return fail(AB200_ETIMEOUT, "a bounded wait ran out in a kernel (site %d)", *status_host);
+  }
   return AB200_OK;
 }

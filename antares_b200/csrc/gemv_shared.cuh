@@ -1,0 +1,91 @@
+// Pieces shared by the two W4A16 decode GEMV kernels (scalar-pipe and warp-MMA).
+#pragma once
+#include <cooperative_groups.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace ab200 {
+
+constexpr int TILE_N = 128;   // columns per CTA: 32 lanes x 4
+constexpr int UNIT_ROWS = 4;  // packed rows per work unit
+constexpr int UNIT_K = UNIT_ROWS * 8;
+
+// Epilogues: fp16 store; fp32 residual += fp16-rounded result; fp32 store (tensor-parallel partials).
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_STORE_F32 = 2 };
+
+// (q-8) for the eight nibbles of `w` as four half2: (n0,n4) (n1,n5) (n2,n6) (n3,n7).
+// 0x6400 | q is the fp16 number 1024+q; the high nibble of each byte gives 1024+16q, brought
+// back with one HFMA2 (x/16 - 72), so only one shift is needed per word.
+__device__ __forceinline__ void unpack8(uint32_t w, __half2 (&v)[4]) {
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
+  const __half2 c1032 = u2h2(0x64086408u);  // (1032, 1032)
+  const __half2 c16th = u2h2(0x2C002C00u);  // (1/16, 1/16)
+  const __half2 cm72 = u2h2(0xD480D480u);   // (-72, -72)
+  const uint32_t w8 = w >> 8;
+  const uint32_t t0 = lop3<0xEA>(w, LO, MAGIC);  // (a & b) | c
+  const uint32_t t1 = lop3<0xEA>(w, HI, MAGIC);
+  const uint32_t t2 = lop3<0xEA>(w8, LO, MAGIC);
+  const uint32_t t3 = lop3<0xEA>(w8, HI, MAGIC);
+  v[0] = __hsub2(u2h2(t0), c1032);
+  v[1] = __hfma2(u2h2(t1), c16th, cm72);
+  v[2] = __hsub2(u2h2(t2), c1032);
+  v[3] = __hfma2(u2h2(t3), c16th, cm72);
+}
+
+// Cross-warp, then cross-CTA (cluster) reduction of per-thread fp32 partials, and the epilogue.
+// Warps 0..NWARPS-1 hold partials (facc[m][c] for columns lane*4+c); every thread of the CTA
+// must call this (it contains CTA and cluster barriers).  The order of every sum is fixed, so
+// results are bitwise repeatable.  red: [NWARPS][M][128] floats, part: [M][128] floats.
+template <int M, int EPI, int NTHREADS, int NWARPS>
+__device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red, float *part, void *out, int N, int tile_n0) {
+  namespace cg = cooperative_groups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp < NWARPS) {
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+      *reinterpret_cast<float4 *>(&red[(warp * M + m) * TILE_N + lane * 4]) = make_float4(facc[m][0], facc[m][1], facc[m][2], facc[m][3]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < M * TILE_N; i += NTHREADS) {
+    const int m = i / TILE_N, c = i % TILE_N;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) s += red[(w * M + m) * TILE_N + c];
+    part[i] = s;
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned cs = cluster.num_blocks();
+  if (cs > 1) cluster.sync(); else __syncthreads();
+  const unsigned rank = cluster.block_rank();
+  const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
+  for (int i = threadIdx.x; i < M * cols_per; i += NTHREADS) {
+    const int m = i / cols_per, c = rank * cols_per + i % cols_per;
+    float s = 0.f;
+    for (unsigned r = 0; r < cs; ++r) {
+      const float *remote = (cs > 1) ? cluster.map_shared_rank(part, r) : part;
+      s += remote[m * TILE_N + c];
+    }
+    const int n = tile_n0 + c;
+    if (n < N) {
+      if (EPI == EPI_STORE) {
+        reinterpret_cast<__half *>(out)[(size_t)m * N + n] = __float2half_rn(s);
+      } else if (EPI == EPI_STORE_F32) {
+        reinterpret_cast<float *>(out)[(size_t)m * N + n] = s;
+      } else {
+        float *o = reinterpret_cast<float *>(out) + (size_t)m * N + n;
+        *o += __half2float(__float2half_rn(s));
+      }
+    }
+  }
+  if (cs > 1) cluster.sync();  // keep `part` alive until every peer has read it
+}
+
+// warp-MMA variant (w4a16_gemv_mma.cu)
+bool gemv_mma_eligible(int dtype, int M);
+int gemv_mma_dispatch(const void *x, const int32_t *qw, const void *scales, void *out, int M, int K, int N, int group, int epi,
+                      cudaStream_t s);
+int gemv_tuning_set(const char *name, int value);
+int gemv_tuning_cluster();
+
+}  // namespace ab200

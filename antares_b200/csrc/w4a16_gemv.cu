@@ -1,4 +1,6 @@
 // W4A16 decode GEMV for sm_100a: out[M,N] = x[M,K] . dequant(qweight[K/8,N], scales[K/group,N]).
+// Scalar-pipe variant (no tensor cores) for fp16, selectable with option gemv_impl=1, and the
+// fp32 variant; the default fp16 path is the warp-MMA kernel in w4a16_gemv_mma.cu.
 //
 // Replaces the kernel the reference generates from samples/05_llama2_7b_int4.py:135-139.
 //
@@ -19,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "gemv_shared.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -26,11 +29,6 @@ namespace ab200 {
 
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int TILE_N = 128;  // 32 lanes x 4 columns
-constexpr int UNIT_ROWS = 4; // packed rows per unit
-constexpr int UNIT_K = UNIT_ROWS * 8;
-
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1 };
 
 struct GemvParams {
   const void *x;
@@ -38,69 +36,9 @@ struct GemvParams {
   const void *scales;
   void *out;
   int K, N, group;
-  int units;  // K / 32
+  int units;      // K / 32
+  int xs_stride;  // elements between batch rows of x in shared memory (same in every CTA of a cluster)
 };
-
-// (q-8) for the eight nibbles of `w` as four half2: (n0,n4) (n1,n5) (n2,n6) (n3,n7).
-__device__ __forceinline__ void unpack8(uint32_t w, __half2 (&v)[4]) {
-  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;  // 1024.0 | bits
-  const __half2 c1032 = __half2half2(__ushort_as_half(0x6408));  // 1032
-  const __half2 c16th = __half2half2(__ushort_as_half(0x2C00));  // 1/16
-  const __half2 cm72 = __half2half2(__ushort_as_half(0xD480));   // -72
-  uint32_t w8 = w >> 8;
-  uint32_t t0 = lop3<0xEA>(w, LO, MAGIC);   // (a & b) | c
-  uint32_t t1 = lop3<0xEA>(w, HI, MAGIC);   // 1024 + 16 q
-  uint32_t t2 = lop3<0xEA>(w8, LO, MAGIC);
-  uint32_t t3 = lop3<0xEA>(w8, HI, MAGIC);
-  v[0] = __hsub2(u2h2(t0), c1032);
-  v[1] = __hfma2(u2h2(t1), c16th, cm72);
-  v[2] = __hsub2(u2h2(t2), c1032);
-  v[3] = __hfma2(u2h2(t3), c16th, cm72);
-}
-
-// Cross-warp, then cross-CTA (cluster) reduction of per-thread partials and the epilogue.
-// red: [WARPS][M][128] floats, part: [M][128] floats, both in this CTA's shared memory.
-template <int M, int EPI, typename OutT>
-__device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red, float *part,
-                                                 OutT *out, int N, int tile_n0) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int m = 0; m < M; ++m)
-    *reinterpret_cast<float4 *>(&red[(warp * M + m) * TILE_N + lane * 4]) =
-        make_float4(facc[m][0], facc[m][1], facc[m][2], facc[m][3]);
-  __syncthreads();
-  for (int i = threadIdx.x; i < M * TILE_N; i += GEMV_THREADS) {
-    const int m = i / TILE_N, c = i % TILE_N;
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < GEMV_WARPS; ++w) s += red[(w * M + m) * TILE_N + c];
-    part[i] = s;
-  }
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned cs = cluster.num_blocks();
-  if (cs > 1) cluster.sync(); else __syncthreads();
-  const unsigned rank = cluster.block_rank();
-  const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
-  for (int i = threadIdx.x; i < M * cols_per; i += GEMV_THREADS) {
-    const int m = i / cols_per, c = rank * cols_per + i % cols_per;
-    float s = 0.f;
-    for (unsigned r = 0; r < cs; ++r) {
-      const float *remote = (cs > 1) ? cluster.map_shared_rank(part, r) : part;
-      s += remote[m * TILE_N + c];
-    }
-    const int n = tile_n0 + c;
-    if (n < N) {
-      if (EPI == EPI_STORE) {
-        if (sizeof(OutT) == 2) reinterpret_cast<__half *>(out)[(size_t)m * N + n] = __float2half_rn(s);
-        else reinterpret_cast<float *>(out)[(size_t)m * N + n] = s;
-      } else {
-        float *o = reinterpret_cast<float *>(out) + (size_t)m * N + n;
-        *o += __half2float(__float2half_rn(s));
-      }
-    }
-  }
-  if (cs > 1) cluster.sync();  // keep `part` alive until every peer has read it
-}
 
 template <int M, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams p) {
@@ -114,7 +52,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 
   const int u_begin = (int)((long)p.units * krank / cs), u_end = (int)((long)p.units * (krank + 1) / cs);
   const int k_begin = u_begin * UNIT_K, kslice = (u_end - u_begin) * UNIT_K;
-  const int xs_stride = kslice;  // halves per batch row
+  const int xs_stride = p.xs_stride;
 
   __half *xs = reinterpret_cast<__half *>(smem_raw);
   float *red = reinterpret_cast<float *>(smem_raw + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));
@@ -214,10 +152,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     u = u2;
   }
 
-  if (EPI == EPI_STORE)
-    reduce_and_store<M, EPI, __half>(facc, red, part, reinterpret_cast<__half *>(p.out), p.N, tile * TILE_N);
-  else
-    reduce_and_store<M, EPI, float>(facc, red, part, reinterpret_cast<float *>(p.out), p.N, tile * TILE_N);
+  reduce_and_store<M, EPI, GEMV_THREADS, GEMV_WARPS>(facc, red, part, p.out, p.N, tile * TILE_N);
 }
 
 // fp32 activations / scales / result: the dtypes the in-tree sample declares
@@ -235,14 +170,15 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams
   const int u_begin = (int)((long)p.units * krank / cs), u_end = (int)((long)p.units * (krank + 1) / cs);
   const int k_begin = u_begin * UNIT_K, kslice = (u_end - u_begin) * UNIT_K;
 
+  const int xs_stride = p.xs_stride;
   float *xs = reinterpret_cast<float *>(smem_raw);
-  float *red = xs + (size_t)M * kslice;
+  float *red = xs + (size_t)M * xs_stride;
   float *part = red + GEMV_WARPS * M * TILE_N;
 
   const float *xg = reinterpret_cast<const float *>(p.x);
   for (int i = threadIdx.x; i < M * (kslice / 4); i += GEMV_THREADS) {
     const int m = i / (kslice / 4), r = i % (kslice / 4);
-    *reinterpret_cast<float4 *>(xs + (size_t)m * kslice + r * 4) =
+    *reinterpret_cast<float4 *>(xs + (size_t)m * xs_stride + r * 4) =
         *reinterpret_cast<const float4 *>(xg + (size_t)m * p.K + k_begin + r * 4);
   }
   __syncthreads();
@@ -270,7 +206,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams
       for (int j = 0; j < 8; ++j) {
         float xv[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m) xv[m] = xu[(size_t)m * kslice + r * 8 + j];
+        for (int m = 0; m < M; ++m) xv[m] = xu[(size_t)m * xs_stride + r * 8 + j];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           // 2^23 + q as a float, minus (2^23 + 8): q - 8 exactly.
@@ -282,12 +218,13 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams
       }
     }
   }
-  reduce_and_store<M, EPI_STORE, float>(facc, red, part, reinterpret_cast<float *>(p.out), p.N, tile * TILE_N);
+  reduce_and_store<M, EPI_STORE_F32, GEMV_THREADS, GEMV_WARPS>(facc, red, part, p.out, p.N, tile * TILE_N);
 }
 
 // ---- host side -------------------------------------------------------------------------------
 
 static int pick_cluster(int tiles, int units) {
+  if (gemv_tuning_cluster() > 0) return gemv_tuning_cluster();
   const int target = 2 * sm_count();
   int cs = 1;
   while (cs < 8 && tiles * cs < target && units / (cs * 2) >= GEMV_WARPS) cs *= 2;
@@ -295,18 +232,16 @@ static int pick_cluster(int tiles, int units) {
 }
 
 template <typename Kern>
-static int launch_gemv(Kern kern, const GemvParams &p, int M, int elt, cudaStream_t stream) {
+static int launch_gemv(Kern kern, GemvParams p, int M, int elt, cudaStream_t stream) {
   const int tiles = (p.N + TILE_N - 1) / TILE_N;
   const int cs = pick_cluster(tiles, p.units);
   const int kslice_max = ((p.units + cs - 1) / cs) * UNIT_K;
+  p.xs_stride = kslice_max;
   size_t smem = (((size_t)M * kslice_max * elt + 15) & ~(size_t)15) +
                 (size_t)(GEMV_WARPS + 1) * M * TILE_N * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: K slice of %d values x M=%d does not fit shared memory", kslice_max, M);
-  if (smem > 48 * 1024) {
-    // Raising the limit is idempotent and cheap; doing it per launch keeps the library stateless
-    // across devices.
-    AB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-  }
+  // Raising the limit is idempotent; doing it per launch keeps the library stateless across devices.
+  if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * cs, 1, 1);
   cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
@@ -335,7 +270,7 @@ static int check_gemv_args(const void *x, const int32_t *qw, const void *scales,
 }
 
 template <int EPI>
-static int gemv_f16_dispatch(GemvParams p, int M, cudaStream_t s) {
+static int gemv_f16_direct(GemvParams p, int M, cudaStream_t s) {
   // Batches above 4 re-stream the weights per group of 4 rows.
   const size_t out_elt = (EPI == EPI_STORE) ? sizeof(__half) : sizeof(float);
   for (int m0 = 0; m0 < M; m0 += 4) {
@@ -355,6 +290,15 @@ static int gemv_f16_dispatch(GemvParams p, int M, cudaStream_t s) {
   return AB200_OK;
 }
 
+static int gemv_f16(const void *x, const int32_t *qw, const void *scales, void *out, int M, int K, int N, int group, int epi,
+                    cudaStream_t s) {
+  if (gemv_mma_eligible(AB200_F16, M)) return gemv_mma_dispatch(x, qw, scales, out, M, K, N, group, epi, s);
+  GemvParams p{x, qw, scales, out, K, N, group, K / UNIT_K, 0};
+  if (epi == EPI_STORE) return gemv_f16_direct<EPI_STORE>(p, M, s);
+  if (epi == EPI_RESIDUAL) return gemv_f16_direct<EPI_RESIDUAL>(p, M, s);
+  return gemv_f16_direct<EPI_STORE_F32>(p, M, s);
+}
+
 static int gemv_f32_dispatch(GemvParams p, int M, cudaStream_t s) {
   for (int m0 = 0; m0 < M; m0 += 2) {
     const int mc = (M - m0 < 2) ? (M - m0) : 2;
@@ -368,6 +312,12 @@ static int gemv_f32_dispatch(GemvParams p, int M, cudaStream_t s) {
   return AB200_OK;
 }
 
+// x_f32[i] += fp16_round(partial_f32[i]): the residual update after a tensor-parallel all-reduce.
+__global__ void residual_add_kernel(float *__restrict__ x, const float *__restrict__ partial, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    x[i] += __half2float(__float2half_rn(partial[i]));
+}
+
 }  // namespace ab200
 
 using namespace ab200;
@@ -376,9 +326,11 @@ extern "C" int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const voi
                                 int M, int K, int N, int group, int dtype, void *stream) {
   clear_error();
   if (int rc = check_gemv_args(x, qweight, scales, out, M, K, N, group)) return rc;
-  GemvParams p{x, qweight, scales, out, K, N, group, K / UNIT_K};
-  if (dtype == AB200_F16) return gemv_f16_dispatch<EPI_STORE>(p, M, (cudaStream_t)stream);
-  if (dtype == AB200_F32) return gemv_f32_dispatch(p, M, (cudaStream_t)stream);
+  if (dtype == AB200_F16) return gemv_f16(x, qweight, scales, out, M, K, N, group, EPI_STORE, (cudaStream_t)stream);
+  if (dtype == AB200_F32) {
+    GemvParams p{x, qweight, scales, out, K, N, group, K / UNIT_K, 0};
+    return gemv_f32_dispatch(p, M, (cudaStream_t)stream);
+  }
   return fail(AB200_EINVAL, "w4a16_gemv: unknown dtype %d", dtype);
 }
 
@@ -386,6 +338,26 @@ extern "C" int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, 
                                          float *resid_f32, int M, int K, int N, int group, void *stream) {
   clear_error();
   if (int rc = check_gemv_args(x, qweight, scales, resid_f32, M, K, N, group)) return rc;
-  GemvParams p{x, qweight, scales, resid_f32, K, N, group, K / UNIT_K};
-  return gemv_f16_dispatch<EPI_RESIDUAL>(p, M, (cudaStream_t)stream);
+  return gemv_f16(x, qweight, scales, resid_f32, M, K, N, group, EPI_RESIDUAL, (cudaStream_t)stream);
+}
+
+extern "C" int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, const void *scales,
+                                       float *out_f32, int M, int K, int N, int group, void *stream) {
+  clear_error();
+  if (int rc = check_gemv_args(x, qweight, scales, out_f32, M, K, N, group)) return rc;
+  return gemv_f16(x, qweight, scales, out_f32, M, K, N, group, EPI_STORE_F32, (cudaStream_t)stream);
+}
+
+extern "C" int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream) {
+  clear_error();
+  AB200_REQUIRE(x_f32 && partial_f32 && n > 0, "residual_add: bad argument");
+  residual_add_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(x_f32, partial_f32, n);
+  AB200_CHECK_LAUNCH("residual_add");
+  return AB200_OK;
+}
+
+extern "C" int ab200_set_option(const char *name, int value) {
+  clear_error();
+  AB200_REQUIRE(name != nullptr, "set_option: null name");
+  return gemv_tuning_set(name, value);
 }

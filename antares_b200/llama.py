@@ -1,0 +1,274 @@
+"""Llama-2-7B-architecture int4 greedy decode built from the antares_b200 operators.
+
+Mirrors the reference's model script samples/05_llama2_7b_int4.py:146-207 (`forward`, decode
+loop) with these B200-first differences:
+  * one decode step = one CUDA graph (captured once, replayed per token); token id, position and
+    the generated ids live in device memory, so the loop needs no host round trip
+    (the reference syncs on `int(torch.argmax(logits))` every token, line 200);
+  * the residual stream is fp32, projection inputs/outputs fp16, KV cache fp16;
+  * RMSNorm computes its own sum of squares; residual adds are fused into the O/down GEMV;
+  * tensor parallel over `world` GPUs: column-parallel V|Q|K and gate|up, row-parallel O and
+    down with one all-reduce each, vocabulary-parallel classifier with an all-gather.
+Weights are seeded synthetic stand-ins for the GPTQ checkpoint (same shapes and value ranges).
+"""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import packing
+from ._lib import call
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    dim: int = 4096
+    n_heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    max_seq: int = 512
+    eps: float = 1e-6
+    rope_base: float = 10000.0
+    group: int = 128
+
+    @property
+    def head_dim(self):
+        return self.dim // self.n_heads
+
+
+# projection ids for seeding: seed = 1000 * layer + id
+_V, _Q, _K, _O, _GATE, _UP, _DOWN, _NORM = range(8)
+
+
+def synth_layer(cfg, layer):
+    """Unsharded synthetic weights of one layer (numpy)."""
+    d, f, g = cfg.dim, cfg.ffn, cfg.group
+    s = 1000 * layer
+    w = {}
+    parts = [packing.synth_w4(d, d, s + i, g) for i in (_V, _Q, _K)]
+    w["vqk_q"] = np.ascontiguousarray(np.concatenate([p[0] for p in parts], axis=1))  # order V, Q, K (line 27)
+    w["vqk_s"] = np.ascontiguousarray(np.concatenate([p[1] for p in parts], axis=1))
+    w["o_q"], w["o_s"] = packing.synth_w4(d, d, s + _O, g)
+    w["gate_q"], w["gate_s"] = packing.synth_w4(d, f, s + _GATE, g)
+    w["up_q"], w["up_s"] = packing.synth_w4(d, f, s + _UP, g)
+    w["down_q"], w["down_s"] = packing.synth_w4(f, d, s + _DOWN, g)
+    rng = np.random.default_rng(s + _NORM)
+    w["att_norm"] = (1 + 0.1 * rng.standard_normal(d, dtype=np.float32)).astype(np.float16)
+    w["ffn_norm"] = (1 + 0.1 * rng.standard_normal(d, dtype=np.float32)).astype(np.float16)
+    return w
+
+
+def _f16(a_f32):
+    # IEEE round-to-nearest-even like numpy's astype, but multithreaded (numpy's is scalar).
+    return torch.from_numpy(a_f32).to(torch.float16).numpy()
+
+
+def synth_globals(cfg):
+    rng = np.random.default_rng(999983)
+    def table():
+        a = rng.standard_normal((cfg.vocab, cfg.dim), dtype=np.float32)
+        a *= np.float32(0.02)
+        return _f16(a)
+    return {"embed": table(), "lm_head": table(),
+            "final_norm": (1 + 0.1 * rng.standard_normal(cfg.dim, dtype=np.float32)).astype(np.float16)}
+
+
+def synth_prompt(cfg, n, seed=0):
+    return np.random.default_rng(seed).integers(3, cfg.vocab, size=n).astype(np.int32)
+
+
+def make_inv_freq(head_dim, base):
+    j = np.arange(0, head_dim, 2, dtype=np.float32)
+    f = (1.0 / (np.float32(base) ** (j / np.float32(head_dim)))).astype(np.float32)
+    return np.concatenate([f, f]).astype(np.float32)  # length head_dim, halves equal (lines 125-126)
+
+
+def shard_layer(cfg, w, rank, world):
+    """Per-rank slices of one layer's weights."""
+    d, g = cfg.dim, cfg.group
+    dl = d // world
+    sl = slice(rank * dl, (rank + 1) * dl)
+    out = {}
+    out["vqk_q"] = np.ascontiguousarray(np.concatenate([w["vqk_q"][:, i * d:(i + 1) * d][:, sl] for i in range(3)], axis=1))
+    out["vqk_s"] = np.ascontiguousarray(np.concatenate([w["vqk_s"][:, i * d:(i + 1) * d][:, sl] for i in range(3)], axis=1))
+    out["o_q"] = np.ascontiguousarray(w["o_q"][rank * dl // 8:(rank + 1) * dl // 8])
+    out["o_s"] = np.ascontiguousarray(w["o_s"][rank * dl // g:(rank + 1) * dl // g])
+    k0, k1 = packing.row_shard_bounds(cfg.ffn, world, g)[rank]
+    out["gu_q"] = np.ascontiguousarray(np.concatenate([w["gate_q"][:, k0:k1], w["up_q"][:, k0:k1]], axis=1))
+    out["gu_s"] = np.ascontiguousarray(np.concatenate([w["gate_s"][:, k0:k1], w["up_s"][:, k0:k1]], axis=1))
+    out["down_q"] = np.ascontiguousarray(w["down_q"][k0 // 8:k1 // 8])
+    out["down_s"] = np.ascontiguousarray(w["down_s"][k0 // g:k1 // g])
+    out["att_norm"], out["ffn_norm"] = w["att_norm"], w["ffn_norm"]
+    return out
+
+
+class LlamaInt4Decoder:
+    """Greedy decoder for one rank of a tensor-parallel group (world=1: the whole model).
+
+    `comm` is None for world=1, otherwise an object with
+      all_reduce_sum_(t_f32)  and  all_gather_into(out, t)   (see parallel.py).
+    """
+
+    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024):
+        assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
+        self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
+        self.hl = cfg.n_heads // world            # local heads
+        self.dl = cfg.dim // world                # local attention width
+        k0, k1 = packing.row_shard_bounds(cfg.ffn, world, cfg.group)[rank]
+        self.fl = k1 - k0                         # local FFN width
+        self.vl = cfg.vocab // world
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        self.layers = []
+        for l in range(cfg.n_layers):
+            w = shard_layer(cfg, synth_layer(cfg, l), rank, world)
+            self.layers.append({k: t(v) for k, v in w.items()})
+        gl = synth_globals(cfg)
+        self.embed = t(gl["embed"])
+        self.lm_head = t(gl["lm_head"][rank * self.vl:(rank + 1) * self.vl])
+        self.final_norm = t(gl["final_norm"])
+        self.inv_freq = t(make_inv_freq(cfg.head_dim, cfg.rope_base))
+        z = lambda *s, dt=torch.float16: torch.zeros(*s, dtype=dt, device=device)
+        self.k_cache = z(cfg.n_layers, cfg.max_seq, self.dl)
+        self.v_cache = z(cfg.n_layers, cfg.max_seq, self.dl)
+        self.x = z(cfg.dim, dt=torch.float32)
+        self.xb = z(cfg.dim)
+        self.vqk = z(3 * self.dl)
+        self.q = z(self.dl)
+        self.att = z(self.dl)
+        self.gu = z(2 * self.fl)
+        self.h = z(self.fl)
+        self.partial = z(cfg.dim, dt=torch.float32)
+        self.logits_local = z(self.vl, dt=torch.float32)
+        self.logits = self.logits_local if world == 1 else z(cfg.vocab, dt=torch.float32)
+        self.token = torch.zeros(1, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.max_tokens = max_tokens
+        self.prompt = torch.zeros(max_tokens, dtype=torch.int32, device=device)
+        self.out_tokens = torch.zeros(max_tokens + 1, dtype=torch.int32, device=device)
+        self.n_prompt = 0
+        self.att_scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.graph = None
+        self.launches_per_step = 0
+        self._pin_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    # -- one decode step, eager (enqueues every kernel on the current stream) --------------------
+    def _gemv(self, x, q, s, out):
+        K, N = q.shape[0] * 8, q.shape[1]
+        call("ab200_w4a16_gemv", x.data_ptr(), q.data_ptr(), s.data_ptr(), out.data_ptr(), 1, K, N, self.cfg.group, 0, self._st)
+        self._n += 1
+
+    def _gemv_out_proj(self, x, q, s):
+        """Row-parallel projection + residual: fused when alone, all-reduce of fp32 partials otherwise."""
+        K, N = q.shape[0] * 8, q.shape[1]
+        if self.world == 1:
+            call("ab200_w4a16_gemv_residual", x.data_ptr(), q.data_ptr(), s.data_ptr(), self.x.data_ptr(), 1, K, N, self.cfg.group, self._st)
+            self._n += 1
+        else:
+            call("ab200_w4a16_gemv_f32out", x.data_ptr(), q.data_ptr(), s.data_ptr(), self.partial.data_ptr(), 1, K, N, self.cfg.group, self._st)
+            self.comm.all_reduce_sum_(self.partial)
+            call("ab200_residual_add", self.x.data_ptr(), self.partial.data_ptr(), N, self._st)
+            self._n += 3
+
+    def _rmsnorm(self, weight):
+        call("ab200_rmsnorm", self.x.data_ptr(), 1, weight.data_ptr(), self.xb.data_ptr(), 1, self.cfg.dim, self.cfg.eps, self._st)
+        self._n += 1
+
+    def step_eager(self):
+        cfg = self.cfg
+        self._st = torch.cuda.current_stream().cuda_stream
+        self._n = 0
+        st = self._st
+        call("ab200_embed_lookup", self.embed.data_ptr(), self.token.data_ptr(), self.x.data_ptr(), cfg.dim, cfg.vocab, st)
+        self._n += 1
+        for l, w in enumerate(self.layers):
+            self._rmsnorm(w["att_norm"])
+            self._gemv(self.xb, w["vqk_q"], w["vqk_s"], self.vqk)
+            call("ab200_rope_kv_store", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), self.q.data_ptr(),
+                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.hl, cfg.head_dim, self.dl, cfg.max_seq, st)
+            call("ab200_attention_decode", self.q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
+                 self.att.data_ptr(), self.pos.data_ptr(), 1, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
+            self._n += 2
+            self._gemv_out_proj(self.att, w["o_q"], w["o_s"])
+            self._rmsnorm(w["ffn_norm"])
+            self._gemv(self.xb, w["gu_q"], w["gu_s"], self.gu)
+            call("ab200_silu_mul", self.gu.data_ptr(), self.h.data_ptr(), self.fl, st)
+            self._n += 1
+            self._gemv_out_proj(self.h, w["down_q"], w["down_s"])
+        self._rmsnorm(self.final_norm)
+        call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), cfg.dim, self.vl, st)
+        self._n += 1
+        if self.world > 1:
+            self.comm.all_gather_into(self.logits, self.logits_local)
+            self._n += 1
+        call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), self._n_prompt_capture,
+             self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), st)
+        self._n += 1
+        self.launches_per_step = self._n
+
+    # -- graph ---------------------------------------------------------------------------------------
+    def capture(self, n_prompt):
+        """Captures one step as a CUDA graph.  n_prompt is baked into the graph (the argmax kernel
+        forces prompt tokens while pos + 1 < n_prompt)."""
+        self._n_prompt_capture = int(n_prompt)
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.reset(self.prompt[:max(n_prompt, 1)].clone())
+            for _ in range(2):  # warm-up outside capture (first-use attribute calls, NCCL setup)
+                self.step_eager()
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self.step_eager()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return self
+
+    def reset(self, prompt_dev):
+        """Start a new sequence: pos = 0, token = prompt[0]."""
+        n = int(prompt_dev.numel())
+        assert 1 <= n <= self.max_tokens
+        self.n_prompt = n
+        self.prompt[:n].copy_(prompt_dev)
+        self.token.copy_(self.prompt[:1])
+        self.pos.zero_()
+        self.out_tokens.zero_()
+        self.out_tokens[:1].copy_(self.prompt[:1])
+
+    def generate(self, prompt, n_new):
+        """Feeds the prompt token by token (as the reference does, lines 194-200) and generates
+        n_new tokens greedily.  Returns all n_prompt + n_new token ids (numpy)."""
+        prompt = np.asarray(prompt, np.int32)
+        n_prompt = len(prompt)
+        total = n_prompt + n_new
+        assert total <= self.cfg.max_seq + 1 and total <= self.max_tokens
+        if self.graph is None or self._n_prompt_capture != n_prompt:
+            self.prompt[:n_prompt].copy_(torch.from_numpy(prompt))
+            self.capture(n_prompt)
+        self.reset(torch.from_numpy(prompt).to(self.dev))
+        for _ in range(total - 1):
+            self.graph.replay()
+        torch.cuda.synchronize()
+        return self.out_tokens[:total].cpu().numpy()
+
+    def step(self, token):
+        """Public per-token call with HOST token ids: copies the id in, runs one step, copies the
+        chosen id out.  Position advances on the device."""
+        self._pin_in[0] = int(token)
+        self.token.copy_(self._pin_in, non_blocking=True)
+        self.graph.replay()
+        self._pin_out.copy_(self.token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(self._pin_out[0])
+
+    # bytes one step must move through HBM on this rank (the roofline numerator for decode)
+    def step_bytes(self, pos):
+        cfg, g = self.cfg, self.cfg.group
+        def lin(K, N):
+            return K * N // 2 + (K // g) * N * 2 + K * 2 + N * 2
+        per_layer = lin(cfg.dim, 3 * self.dl) + lin(self.dl, cfg.dim) + lin(cfg.dim, 2 * self.fl) + lin(self.fl, cfg.dim)
+        per_layer += 2 * (pos + 1) * self.dl * 2  # K and V rows read by attention
+        return cfg.n_layers * per_layer + self.vl * cfg.dim * 2

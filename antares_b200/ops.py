@@ -164,7 +164,7 @@ def softmax(x, out=None):
     return out
 
 
-def attention_decode(q, k_cache, v_cache, seq_len_dev, scale, out=None, kv_stride=None, max_seq=None):
+def attention_decode(q, k_cache, v_cache, seq_len_dev, scale, out=None, kv_stride=None, max_seq=None, seq_len_add=0):
     H, D = q.shape
     if kv_stride is None:
         kv_stride = k_cache.stride(0)
@@ -173,6 +173,19 @@ def attention_decode(q, k_cache, v_cache, seq_len_dev, scale, out=None, kv_strid
     if out is None:
         out = torch.empty_like(q)
     call("ab200_attention_decode", _chk(q, "q", torch.float16), k_cache.data_ptr(), v_cache.data_ptr(),
-         _chk(out, "out", torch.float16), _chk(seq_len_dev, "seq_len_dev", torch.int32), int(max_seq), H, D,
+         _chk(out, "out", torch.float16), _chk(seq_len_dev, "seq_len_dev", torch.int32), int(seq_len_add), int(max_seq), H, D,
          int(kv_stride), float(scale), _stream())
     return out
+
+
+def set_option(name, value):
+    """Process-wide tuning knob (gemv_cluster, gemv_impl)."""
+    call("ab200_set_option", name.encode(), int(value))
+
+
+def kernel_status():
+    """Reads and clears the device status word; raises Ab200Error(ETIMEOUT) if a bounded wait ran out."""
+    import ctypes
+    v = ctypes.c_int(0)
+    call("ab200_kernel_status", ctypes.cast(ctypes.pointer(v), ctypes.c_void_p))
+    return v.value

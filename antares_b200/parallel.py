@@ -1,0 +1,56 @@
+"""Tensor-parallel plumbing: one process per GPU, torch.distributed over NCCL (NVLink / NVSwitch).
+
+The reference has no tensor-parallel path for this model (its samples are single-device); its
+only collectives are the TensorFlow plugin's NCCL calls (frameworks/tensorflow/communicate_ops.cc:
+191-193: all-reduce, reduce-scatter, all-gather over flat tensors).  The decode step needs two of
+them: sum all-reduce of the [dim] fp32 partials after the row-parallel projections, and an
+all-gather of vocabulary-shard logits.
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def init_from_env(backend=None):
+    """Joins the process group described by RANK / WORLD_SIZE / MASTER_* (as set by torchrun).
+    Returns (rank, world, local_rank)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        kw = {}
+        if backend == "nccl":
+            torch.cuda.set_device(local_rank)
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, **kw)
+    return rank, world, local_rank
+
+
+class TorchComm:
+    """Collectives the decoder needs, on a torch.distributed process group (NCCL on GPUs, gloo
+    for the CPU tests).  Both calls are legal inside CUDA graph capture with NCCL."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def all_reduce_sum_(self, t):
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def all_gather_into(self, out, t):
+        dist.all_gather_into_tensor(out, t, group=self.group)
+        return out
+
+    def barrier(self):
+        dist.barrier(group=self.group)
+
+    def max_float(self, v, device):
+        t = torch.tensor([float(v)], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())

@@ -40,6 +40,18 @@ enum { AB200_F16 = 0, AB200_F32 = 1 };
 const char *ab200_last_error(void);
 int ab200_abi_version(void);
 
+/* Reads and clears the device-side status word.  Kernels that wait on barriers bound every
+ * wait; a wait that ran out leaves a site code here instead of hanging (the reference has a
+ * host watchdog that exits the process, graph_evaluator/run_graph.cpp:59-73).  Returns
+ * AB200_ETIMEOUT if the word was set.  Synchronises the device; not legal during capture. */
+int ab200_kernel_status(int *status_host);
+
+/* Tuning knobs, the counterpart of the `config=` hints of autort.export
+ * (samples/05_llama2_7b_int4.py:139).  Names: "gemv_cluster" (0 = auto, 1/2/4/8 K-slices per
+ * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 warp MMA), "gemv_depth" (0 auto, 2..6 units of
+ * prefetch per warp in the warp-MMA kernel).  Process-wide; host call. */
+int ab200_set_option(const char *name, int value);
+
 /* Device property probe; replaces engine/cuda_properties.cc:35-52 (which prints
  * key/value pairs for the code generator).  Fills 8 ints:
  * [0] SM count, [1] max shared memory per block (opt-in, bytes), [2] L2 bytes,
@@ -68,7 +80,7 @@ int ab200_w4_dequant(const int32_t *qweight, const void *scales, int K, int N, i
 /* ---- W4A16 contraction --------------------------------------------------------------------
  * out[M, N] = sum_S x[M, S] * (scales[S/group, N] * (q[S, N] - 8)), fp32 accumulation —
  * the exported op `my_custom_fn` of samples/05_llama2_7b_int4.py:135-144 (`matmul_dequat`).
- * This is the decode path (M <= 16): weights are streamed once from HBM, no tensor cores.
+ * This is the decode path (M <= 16): weights are streamed once from HBM.
  * Constraints: K % 32 == 0, group % 32 == 0, K % group == 0, N % 4 == 0, 1 <= M <= 16,
  * pointers 16-byte aligned. */
 int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const void *scales, void *out, int M,
@@ -79,6 +91,16 @@ int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const void *scales, 
  * replaces `xb = matmul_dequat(...); x = x + xb`, samples/05_llama2_7b_int4.py:167-168,172-173. */
 int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, const void *scales,
                               float *resid_f32, int M, int K, int N, int group, void *stream);
+
+/* Same contraction, fp16 inputs, unrounded fp32 result: the per-rank partial sum of a
+ * row-parallel projection, to be all-reduced and then added with ab200_residual_add.
+ * (Tensor-parallel decode has no counterpart in the reference: its samples are single-device.) */
+int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, const void *scales,
+                            float *out_f32, int M, int K, int N, int group, void *stream);
+
+/* x_f32[i] += fp16_round(partial_f32[i]) — the residual update of lines 168,173 applied to an
+ * all-reduced partial. */
+int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream);
 
 /* Prefill contraction on tensor cores (tcgen05 + TMEM): same arithmetic, M a multiple of 128.
  * Replaces the same exported op called with a leading M axis. */
@@ -112,11 +134,11 @@ int ab200_softmax(const void *x, void *out, int rows, int cols, int dtype, void 
 
 /* autort.ops.attention_f32(q[H,D], K[S,H,D], V[S,H,D], att_f[1]) — call site
  * samples/05_llama2_7b_int4.py:161-165.  fp16 q/K/V/out, fp32 math.  The number of cache rows
- * attended is S = *seq_len_dev (a device int, so a captured graph can be replayed as the
+ * attended is S = *seq_len_dev + seq_len_add (a device int, so a captured graph can be replayed as the
  * sequence grows); kv_stride = elements between consecutive cache rows; D == 128. */
 int ab200_attention_decode(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16,
-                           void *out_f16, const int32_t *seq_len_dev, int max_seq, int H, int D,
-                           long kv_stride, float scale, void *stream);
+                           void *out_f16, const int32_t *seq_len_dev, int seq_len_add, int max_seq,
+                           int H, int D, long kv_stride, float scale, void *stream);
 
 /* ---- decode-step glue (replaces torch eager ops in samples/05_llama2_7b_int4.py:146-177) -- */
 
