@@ -29,6 +29,7 @@ SIGNATURES = {
     "ab200_w4a16_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_w4a16_gemv_residual": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ab200_w4a16_gemv_f32out": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ab200_w4a16_gemv_fused": [_vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "ab200_residual_add": [_vp, _vp, _i, _vp],
     "ab200_kernel_status": [_vp],
     "ab200_set_option": [ctypes.c_char_p, _i],
@@ -41,11 +42,12 @@ SIGNATURES = {
     "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],
     "ab200_embed_lookup": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_rope_kv_store": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _vp],
+    "ab200_attention_fused": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp],
     "ab200_silu_mul": [_vp, _vp, _i, _vp],
     "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_greedy_next": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp],
 }
-OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version"]
+OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version", "ab200_w4a16_gemv_workspace_bytes"]
 
 _lib = None
 
@@ -65,6 +67,8 @@ def load():
         L.ab200_last_error.restype = ctypes.c_char_p
         L.ab200_last_error.argtypes = []
         L.ab200_abi_version.restype = ctypes.c_int
+        L.ab200_w4a16_gemv_workspace_bytes.restype = ctypes.c_size_t
+        L.ab200_w4a16_gemv_workspace_bytes.argtypes = [_i, _i, _i]
         _lib = L
     return _lib
 

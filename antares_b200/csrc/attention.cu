@@ -2,6 +2,8 @@
 // Both are HBM-bound streams: 16-byte loads, fp32 math, warp-shuffle reductions.
 #include <math_constants.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace ab200 {
@@ -98,6 +100,162 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __h
   }
 }
 
+// Decode-step attention with RoPE and the KV-cache update fused in (replaces the rotary_f32 x2 +
+// attention_f32 chain and the cache aliasing of samples/05_llama2_7b_int4.py:151-165).
+// Grid = heads x SPLITS; the SPLITS CTAs of one head form a cluster, each takes the cache rows
+// s = split, split + SPLITS, ... and they merge their partial softmax (max, sum, weighted V) through
+// distributed shared memory.  Every CTA rotates q and the new k of its head itself (128 values);
+// the CTA that owns row `pos` writes the rotated k and v into the cache and uses its own copy, so
+// nothing is read back from global memory inside the kernel.
+struct AttnFusedParams {
+  const __half *vqk;      // [3 * H * D]: V | Q | K of the current token
+  const float *inv_freq;  // [D/2 or D]
+  const int32_t *pos_dev;
+  __half *kc, *vc;        // [max_seq, kv_stride]
+  __half *out;            // [H * D]
+  int H, max_seq;
+  long kv_stride;
+  float scale;
+  int rows_per_cta;       // ceil(max_seq / SPLITS): capacity of the score buffer
+};
+
+__global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedParams p) {
+  namespace cg = cooperative_groups;
+  extern __shared__ __align__(16) float att_smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int splits = (int)cluster.num_blocks(), split = (int)cluster.block_rank();
+  const int h = blockIdx.x / splits;
+  float *sc = att_smem;                      // [rows_per_cta] scores, then exp weights
+  float *red = sc + p.rows_per_cta;          // [16][128] partial P.V
+  float *part = red + 16 * ATT_D;            // [128 + 2]: this CTA's o (un-normalised), max, sum
+  __shared__ __align__(16) __half q_s[ATT_D], k_s[ATT_D], v_s[ATT_D];
+  __shared__ float sh[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *p.pos_dev;
+  if (pos < 0 || pos >= p.max_seq) {  // out-of-range step: leave cache and output untouched (all CTAs agree)
+    return;
+  }
+  const int S = pos + 1;
+  const int HD = p.H * ATT_D;
+
+  // rotate q and k of this head (rotate-half), keep v
+  if (threadIdx.x < ATT_D / 2) {
+    const int j = threadIdx.x;
+    float sn, cs;
+    sincosf((float)pos * p.inv_freq[j], &sn, &cs);
+    const __half *q = p.vqk + HD + (size_t)h * ATT_D, *k = p.vqk + 2 * HD + (size_t)h * ATT_D;
+    const float qa = __half2float(q[j]), qb = __half2float(q[j + ATT_D / 2]);
+    const float ka = __half2float(k[j]), kb = __half2float(k[j + ATT_D / 2]);
+    q_s[j] = __float2half_rn(qa * cs - qb * sn);
+    q_s[j + ATT_D / 2] = __float2half_rn(qb * cs + qa * sn);
+    k_s[j] = __float2half_rn(ka * cs - kb * sn);
+    k_s[j + ATT_D / 2] = __float2half_rn(kb * cs + ka * sn);
+  } else if (threadIdx.x < ATT_D / 2 + ATT_D / 8) {
+    const int i = threadIdx.x - ATT_D / 2;
+    reinterpret_cast<uint4 *>(v_s)[i] = reinterpret_cast<const uint4 *>(p.vqk + (size_t)h * ATT_D)[i];
+  }
+  __syncthreads();
+  const bool own_new = (pos % splits) == split;
+  if (own_new && threadIdx.x < ATT_D / 8) {
+    reinterpret_cast<uint4 *>(p.kc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(k_s)[threadIdx.x];
+    reinterpret_cast<uint4 *>(p.vc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(v_s)[threadIdx.x];
+  }
+
+  // scores of this CTA's rows: a half-warp per row
+  const int sub = lane & 15, hw = lane >> 4;
+  float qf[8];
+  h8_to_f8(reinterpret_cast<const uint4 *>(q_s)[sub], qf);
+  const __half *kh = p.kc + (size_t)h * ATT_D + sub * 8;
+  const int n_local = (S - split + splits - 1) / splits;  // rows split, split+splits, ... < S
+  float mx = -CUDART_INF_F;
+  for (int i0 = warp * 2; i0 < n_local; i0 += 2 * (ATT_THREADS / 32)) {
+    const int i = i0 + hw;
+    const int s = split + i * splits;
+    float dot = 0.f;
+    if (i < n_local) {
+      float kf[8];
+      const uint4 kv = (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[sub] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
+      h8_to_f8(kv, kf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (i < n_local) {
+      dot *= p.scale;
+      if (sub == 0) sc[i] = dot;
+      mx = fmaxf(mx, dot);
+    }
+  }
+  mx = warp_max(mx);
+  if (lane == 0) sh[warp] = mx;
+  __syncthreads();
+  mx = (lane < ATT_THREADS / 32) ? sh[lane] : -CUDART_INF_F;
+  mx = warp_max(mx);
+  __syncthreads();
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < n_local; i += ATT_THREADS) {
+    const float e = expf(sc[i] - mx);
+    sc[i] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) sh[warp] = sum;
+  __syncthreads();
+  sum = (lane < ATT_THREADS / 32) ? sh[lane] : 0.f;
+  sum = warp_sum(sum);
+
+  // partial P.V: 16 row groups x 16 chunks of 8 dims
+  const int dchunk = threadIdx.x & 15, sgroup = threadIdx.x >> 4;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const __half *vh = p.vc + (size_t)h * ATT_D + dchunk * 8;
+  for (int i = sgroup; i < n_local; i += 16) {
+    const int s = split + i * splits;
+    float vf[8];
+    const uint4 vv = (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[dchunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride);
+    h8_to_f8(vv, vf);
+    const float ps = sc[i];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps, vf[j], acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[sgroup * ATT_D + dchunk * 8 + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.x < ATT_D) {
+    float t = 0.f;
+#pragma unroll
+    for (int gI = 0; gI < 16; ++gI) t += red[gI * ATT_D + threadIdx.x];
+    part[threadIdx.x] = t;
+  }
+  if (threadIdx.x == 0) {
+    part[ATT_D] = mx;
+    part[ATT_D + 1] = sum;
+  }
+  if (splits > 1) cluster.sync(); else __syncthreads();
+  // merge: CTA `split` finalises dims [split*128/splits, ...)
+  const int dims_per = ATT_D / splits;
+  if (threadIdx.x < dims_per) {
+    const int d = split * dims_per + threadIdx.x;
+    float gm = -CUDART_INF_F;
+    for (int r = 0; r < splits; ++r) {
+      const float *rp = (splits > 1) ? cluster.map_shared_rank(part, r) : part;
+      gm = fmaxf(gm, rp[ATT_D]);
+    }
+    float l = 0.f, o = 0.f;
+    for (int r = 0; r < splits; ++r) {
+      const float *rp = (splits > 1) ? cluster.map_shared_rank(part, r) : part;
+      const float w = expf(rp[ATT_D] - gm);  // a CTA without rows has max -inf -> weight 0
+      l += rp[ATT_D + 1] * w;
+      o += rp[d] * w;
+    }
+    p.out[(size_t)h * ATT_D + d] = __float2half_rn(o / l);
+  }
+  if (splits > 1) cluster.sync();
+}
+
 // logits[n] = W[n, :] . x, W fp16 [N, K] row-major (the classifier matmul,
 // samples/05_llama2_7b_int4.py:176).  A warp owns two rows at a time; lanes stride over 16-byte
 // chunks of K; x comes through L1.
@@ -167,5 +325,39 @@ extern "C" int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *log
   dense_gemv_kernel<<<(N + rows_per_block - 1) / rows_per_block, DG_THREADS, 0, (cudaStream_t)stream>>>(
       (const __half *)x_f16, (const __half *)w_f16, logits_f32, K, N);
   AB200_CHECK_LAUNCH("dense_gemv");
+  return AB200_OK;
+}
+
+extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev, void *k_cache_f16,
+                                     void *v_cache_f16, void *out_f16, int H, int D, long kv_stride, int max_seq, float scale,
+                                     void *stream) {
+  clear_error();
+  AB200_REQUIRE(vqk_f16 && inv_freq && pos_dev && k_cache_f16 && v_cache_f16 && out_f16, "attention_fused: null pointer");
+  AB200_REQUIRE(D == ATT_D, "attention_fused: head size %d is not the built size %d", D, ATT_D);
+  AB200_REQUIRE(H > 0 && max_seq > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0, "attention_fused: bad shape H=%d max_seq=%d kv_stride=%ld", H, max_seq, kv_stride);
+  AB200_REQUIRE(aligned16(vqk_f16) && aligned16(k_cache_f16) && aligned16(v_cache_f16) && aligned16(out_f16),
+                "attention_fused: pointers must be 16-byte aligned");
+  int splits = 1;
+  while (splits < 8 && H * splits * 2 <= 2 * sm_count()) splits *= 2;  // up to ~2 CTAs per SM, at most 8 per head
+  AttnFusedParams p{(const __half *)vqk_f16, inv_freq, pos_dev, (__half *)k_cache_f16, (__half *)v_cache_f16, (__half *)out_f16,
+                    H, max_seq, kv_stride, scale, (max_seq + splits - 1) / splits};
+  const size_t smem = ((size_t)p.rows_per_cta + 16 * ATT_D + ATT_D + 2 + 2) * sizeof(float);
+  if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_fused: max_seq=%d exceeds the shared-memory score buffer", max_seq);
+  if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(H * splits, 1, 1);
+  cfg.blockDim = dim3(ATT_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  AB200_CUDA(cudaLaunchKernelEx(&cfg, attention_fused_kernel, p));
   return AB200_OK;
 }

@@ -21,6 +21,10 @@ int fail(int code, const char *fmt, ...) {
 
 void clear_error() { g_err[0] = 0; }
 
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+void pdl_set(bool on) { g_pdl = on; }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -35,6 +35,32 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int sm_count();  // SMs of the current device (cached per device)
 
+// Programmatic dependent launch: when enabled (option "pdl"), kernels are launched with
+// cudaLaunchAttributeProgrammaticStreamSerialization, so a kernel's preamble (weight prefetch)
+// overlaps the tail of the kernel before it; every kernel executes griddepcontrol.wait before
+// touching data an earlier kernel produced.
+bool pdl_enabled();
+void pdl_set(bool on);
+
+// Launch helper: <<<grid, block, smem, stream>>> plus the PDL attribute when enabled.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- device helpers ---------------------------------------------------------------------
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {

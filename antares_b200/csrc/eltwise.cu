@@ -263,9 +263,29 @@ __global__ void __launch_bounds__(1024) greedy_next_kernel(const float *__restri
   __shared__ int si[32];
   float best = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // 16-byte loads, four independent ones in flight per thread; ties keep the lowest index
+  const int nvec = ((reinterpret_cast<uintptr_t>(logits) & 15u) == 0) ? n / 4 : 0;
+  for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * blockDim.x;
+      v[u] = (i < nvec) ? reinterpret_cast<const float4 *>(logits)[i] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = (i0 + u * blockDim.x) * 4;
+      const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (e[j] > best || (e[j] == best && i + j < bi)) { best = e[j]; bi = i + j; }
+    }
+  }
+  for (int i = nvec * 4 + threadIdx.x; i < n; i += blockDim.x) {
     const float v = logits[i];
-    if (v > best) { best = v; bi = i; }
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -86,6 +86,15 @@ bool gemv_mma_eligible(int dtype, int M);
 int gemv_mma_dispatch(const void *x, const int32_t *qw, const void *scales, void *out, int M, int K, int N, int group, int epi,
                       cudaStream_t s);
 int gemv_tuning_set(const char *name, int value);
+int gemv_tuning_impl();
+
+// persistent balanced variant (w4a16_gemv_persist.cu)
+enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
+constexpr size_t PERSIST_COUNTER_BYTES = 64 * 1024;  // counters live at the start of the scratch: up to 16384 column tiles
+size_t gemv_persist_scratch_bytes(int M, int K, int N);
+bool gemv_persist_fits(int M, int K, int N);
+int gemv_persist_dispatch(const void *x, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                          int K, int N, int group, int pro, int epi, void *scratch, cudaStream_t s);
 int gemv_tuning_cluster();
 
 }  // namespace ab200

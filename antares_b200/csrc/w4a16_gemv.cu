@@ -38,9 +38,14 @@ struct GemvParams {
   int K, N, group;
   int units;      // K / 32
   int xs_stride;  // elements between batch rows of x in shared memory (same in every CTA of a cluster)
+  const __half *norm_w = nullptr;  // PRO_RMSNORM: fp16 [K]
+  float eps = 0.f;
 };
 
-template <int M, int EPI>
+// PRO selects how x is built in shared memory: plain fp16 x; RMSNorm of an fp32 row (every CTA
+// recomputes the row's sum of squares from L2: 16 KiB for K = 4096); SiLU(gate) * up of an fp16
+// [M, 2K] row.
+template <int M, int EPI, int PRO>
 __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -76,23 +81,75 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     }
   };
 
+  pdl_launch_dependents();
   int u = u_begin + warp;
   if (u < u_end) load_unit(u, 0);  // weights are on their way before x is staged
+  pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
   // (x0,x4)(x1,x5)(x2,x6)(x3,x7): the pairing the nibble unpack produces.
-  {
+  auto permute = [](uint4 v) {
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    return o;
+  };
+  const int rows = kslice / 8;
+  if (PRO == PRO_PLAIN) {
     const __half *xg = reinterpret_cast<const __half *>(p.x);
-    const int rows = kslice / 8;
     for (int i = threadIdx.x; i < M * rows; i += GEMV_THREADS) {
       const int m = i / rows, r = i % rows;
-      uint4 v = *reinterpret_cast<const uint4 *>(xg + (size_t)m * p.K + k_begin + r * 8);
-      uint4 o;
-      o.x = __byte_perm(v.x, v.z, 0x5410);
-      o.y = __byte_perm(v.x, v.z, 0x7632);
-      o.z = __byte_perm(v.y, v.w, 0x5410);
-      o.w = __byte_perm(v.y, v.w, 0x7632);
-      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = o;
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) =
+          permute(*reinterpret_cast<const uint4 *>(xg + (size_t)m * p.K + k_begin + r * 8));
+    }
+  } else if (PRO == PRO_SILU_MUL) {
+    const __half *xg = reinterpret_cast<const __half *>(p.x);
+    for (int i = threadIdx.x; i < M * rows; i += GEMV_THREADS) {
+      const int m = i / rows, r = i % rows;
+      const uint4 gv = *reinterpret_cast<const uint4 *>(xg + (size_t)m * 2 * p.K + k_begin + r * 8);
+      const uint4 uv = *reinterpret_cast<const uint4 *>(xg + (size_t)m * 2 * p.K + p.K + k_begin + r * 8);
+      const uint32_t ga[4] = {gv.x, gv.y, gv.z, gv.w}, ua[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 gf = __half22float2(u2h2(ga[j])), uf = __half22float2(u2h2(ua[j]));
+        o[j] = h22u(__floats2half2_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y));
+      }
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  } else {
+    __shared__ float sh_ss[GEMV_WARPS];
+    const float *xg = reinterpret_cast<const float *>(p.x);
+    const int rowsK = p.K / 8;
+    for (int m = 0; m < M; ++m) {
+      float ss = 0.f;
+      for (int r = threadIdx.x; r < rowsK; r += GEMV_THREADS) {
+        const float4 a = *reinterpret_cast<const float4 *>(xg + (size_t)m * p.K + r * 8);
+        const float4 b = *reinterpret_cast<const float4 *>(xg + (size_t)m * p.K + r * 8 + 4);
+        ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) sh_ss[warp] = ss;
+      __syncthreads();
+      float tot = (lane < GEMV_WARPS) ? sh_ss[lane] : 0.f;
+      tot = warp_sum(tot);
+      __syncthreads();
+      const float rs = rsqrtf(tot * (1.0f / (float)p.K) + p.eps);
+      for (int r = threadIdx.x; r < rows; r += GEMV_THREADS) {
+        const float *xr = xg + (size_t)m * p.K + k_begin + r * 8;
+        const float4 a = *reinterpret_cast<const float4 *>(xr), b = *reinterpret_cast<const float4 *>(xr + 4);
+        const uint4 wv = *reinterpret_cast<const uint4 *>(p.norm_w + k_begin + r * 8);
+        const float2 w0 = __half22float2(u2h2(wv.x)), w1 = __half22float2(u2h2(wv.y)), w2 = __half22float2(u2h2(wv.z)),
+                     w3 = __half22float2(u2h2(wv.w));
+        uint4 o;
+        o.x = h22u(__floats2half2_rn(a.x * rs * w0.x, a.y * rs * w0.y));
+        o.y = h22u(__floats2half2_rn(a.z * rs * w1.x, a.w * rs * w1.y));
+        o.z = h22u(__floats2half2_rn(b.x * rs * w2.x, b.y * rs * w2.y));
+        o.w = h22u(__floats2half2_rn(b.z * rs * w3.x, b.w * rs * w3.y));
+        *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(o);
+      }
     }
   }
   __syncthreads();
@@ -247,13 +304,15 @@ static int launch_gemv(Kern kern, GemvParams p, int M, int elt, cudaStream_t str
   cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cs;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   AB200_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
   return AB200_OK;
 }
@@ -269,34 +328,87 @@ static int check_gemv_args(const void *x, const int32_t *qw, const void *scales,
   return AB200_OK;
 }
 
-template <int EPI>
+template <int EPI, int PRO>
 static int gemv_f16_direct(GemvParams p, int M, cudaStream_t s) {
   // Batches above 4 re-stream the weights per group of 4 rows.
   const size_t out_elt = (EPI == EPI_STORE) ? sizeof(__half) : sizeof(float);
+  const size_t x_row_bytes = (PRO == PRO_RMSNORM) ? (size_t)p.K * 4 : (PRO == PRO_SILU_MUL) ? (size_t)p.K * 4 : (size_t)p.K * 2;
   for (int m0 = 0; m0 < M; m0 += 4) {
     const int mc = (M - m0 < 4) ? (M - m0) : 4;
     GemvParams q = p;
-    q.x = reinterpret_cast<const __half *>(p.x) + (size_t)m0 * p.K;
+    q.x = reinterpret_cast<const char *>(p.x) + (size_t)m0 * x_row_bytes;
     q.out = reinterpret_cast<char *>(p.out) + (size_t)m0 * p.N * out_elt;
     int rc;
     switch (mc) {
-      case 1: rc = launch_gemv(w4a16_gemv_f16_kernel<1, EPI>, q, 1, 2, s); break;
-      case 2: rc = launch_gemv(w4a16_gemv_f16_kernel<2, EPI>, q, 2, 2, s); break;
-      case 3: rc = launch_gemv(w4a16_gemv_f16_kernel<3, EPI>, q, 3, 2, s); break;
-      default: rc = launch_gemv(w4a16_gemv_f16_kernel<4, EPI>, q, 4, 2, s); break;
+      case 1: rc = launch_gemv(w4a16_gemv_f16_kernel<1, EPI, PRO>, q, 1, 2, s); break;
+      case 2: rc = launch_gemv(w4a16_gemv_f16_kernel<2, EPI, PRO>, q, 2, 2, s); break;
+      case 3: rc = launch_gemv(w4a16_gemv_f16_kernel<3, EPI, PRO>, q, 3, 2, s); break;
+      default: rc = launch_gemv(w4a16_gemv_f16_kernel<4, EPI, PRO>, q, 4, 2, s); break;
     }
     if (rc) return rc;
   }
   return AB200_OK;
 }
 
-static int gemv_f16(const void *x, const int32_t *qw, const void *scales, void *out, int M, int K, int N, int group, int epi,
-                    cudaStream_t s) {
-  if (gemv_mma_eligible(AB200_F16, M)) return gemv_mma_dispatch(x, qw, scales, out, M, K, N, group, epi, s);
+// Library-owned scratch for the persistent kernel's K-slice partials and tile counters: one
+// buffer per device, allocated (and zeroed) at the first call that needs it or needs more.
+static void *g_scratch[64] = {nullptr};
+static size_t g_scratch_bytes[64] = {0};
+
+static int library_scratch(size_t bytes, void **out) {
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
+  if (g_scratch_bytes[dev] < bytes) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    (void)cap;
+    size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
+    if (g_scratch[dev]) {
+      AB200_CUDA(cudaDeviceSynchronize());
+      AB200_CUDA(cudaFree(g_scratch[dev]));
+      g_scratch[dev] = nullptr;
+      g_scratch_bytes[dev] = 0;
+    }
+    AB200_CUDA(cudaMalloc(&g_scratch[dev], want));
+    AB200_CUDA(cudaMemset(g_scratch[dev], 0, want));
+    AB200_CUDA(cudaDeviceSynchronize());
+    g_scratch_bytes[dev] = want;
+  }
+  *out = g_scratch[dev];
+  return AB200_OK;
+}
+
+template <int PRO>
+static int gemv_f16_scalar(GemvParams p, int M, int epi, cudaStream_t s) {
+  if (epi == EPI_STORE) return gemv_f16_direct<EPI_STORE, PRO>(p, M, s);
+  if (epi == EPI_RESIDUAL) return gemv_f16_direct<EPI_RESIDUAL, PRO>(p, M, s);
+  return gemv_f16_direct<EPI_STORE_F32, PRO>(p, M, s);
+}
+
+// fp16 path.  Auto choice: batches of 1-2 rows on the scalar-pipe cluster kernel (lowest fixed
+// cost and best streaming rate at that size), 3-16 rows on the persistent warp-MMA kernel (needs
+// scratch; scratch == nullptr means the library-owned buffer), cluster warp-MMA when x does not
+// fit the persistent kernel's shared memory.
+static int gemv_f16(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                    int K, int N, int group, int epi, void *scratch, cudaStream_t s) {
+  const int impl = gemv_tuning_impl();
+  const bool persist_ok = gemv_persist_fits(M, K, N) && N % 4 == 0;
+  if ((impl == 3 || (impl == 0 && M > 2)) && persist_ok) {
+    if (!scratch) {
+      if (int rc = library_scratch(gemv_persist_scratch_bytes(M, K, N), &scratch)) return rc;
+    }
+    return gemv_persist_dispatch(x, norm_w, eps, qw, scales, out, M, K, N, group, pro, epi, scratch, s);
+  }
+  if (impl == 2 || (impl == 0 && M > 2)) {
+    if (pro != PRO_PLAIN) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: fused prologue with M=%d K=%d does not fit the warp-MMA kernels", M, K);
+    return gemv_mma_dispatch(x, qw, scales, out, M, K, N, group, epi, s);
+  }
   GemvParams p{x, qw, scales, out, K, N, group, K / UNIT_K, 0};
-  if (epi == EPI_STORE) return gemv_f16_direct<EPI_STORE>(p, M, s);
-  if (epi == EPI_RESIDUAL) return gemv_f16_direct<EPI_RESIDUAL>(p, M, s);
-  return gemv_f16_direct<EPI_STORE_F32>(p, M, s);
+  p.norm_w = norm_w;
+  p.eps = eps;
+  if (pro == PRO_PLAIN) return gemv_f16_scalar<PRO_PLAIN>(p, M, epi, s);
+  if (pro == PRO_RMSNORM) return gemv_f16_scalar<PRO_RMSNORM>(p, M, epi, s);
+  return gemv_f16_scalar<PRO_SILU_MUL>(p, M, epi, s);
 }
 
 static int gemv_f32_dispatch(GemvParams p, int M, cudaStream_t s) {
@@ -326,7 +438,7 @@ extern "C" int ab200_w4a16_gemv(const void *x, const int32_t *qweight, const voi
                                 int M, int K, int N, int group, int dtype, void *stream) {
   clear_error();
   if (int rc = check_gemv_args(x, qweight, scales, out, M, K, N, group)) return rc;
-  if (dtype == AB200_F16) return gemv_f16(x, qweight, scales, out, M, K, N, group, EPI_STORE, (cudaStream_t)stream);
+  if (dtype == AB200_F16) return gemv_f16(x, PRO_PLAIN, nullptr, 0.f, qweight, scales, out, M, K, N, group, EPI_STORE, nullptr, (cudaStream_t)stream);
   if (dtype == AB200_F32) {
     GemvParams p{x, qweight, scales, out, K, N, group, K / UNIT_K, 0};
     return gemv_f32_dispatch(p, M, (cudaStream_t)stream);
@@ -338,14 +450,31 @@ extern "C" int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, 
                                          float *resid_f32, int M, int K, int N, int group, void *stream) {
   clear_error();
   if (int rc = check_gemv_args(x, qweight, scales, resid_f32, M, K, N, group)) return rc;
-  return gemv_f16(x, qweight, scales, resid_f32, M, K, N, group, EPI_RESIDUAL, (cudaStream_t)stream);
+  return gemv_f16(x, PRO_PLAIN, nullptr, 0.f, qweight, scales, resid_f32, M, K, N, group, EPI_RESIDUAL, nullptr, (cudaStream_t)stream);
 }
 
 extern "C" int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, const void *scales,
                                        float *out_f32, int M, int K, int N, int group, void *stream) {
   clear_error();
   if (int rc = check_gemv_args(x, qweight, scales, out_f32, M, K, N, group)) return rc;
-  return gemv_f16(x, qweight, scales, out_f32, M, K, N, group, EPI_STORE_F32, (cudaStream_t)stream);
+  return gemv_f16(x, PRO_PLAIN, nullptr, 0.f, qweight, scales, out_f32, M, K, N, group, EPI_STORE_F32, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" size_t ab200_w4a16_gemv_workspace_bytes(int M, int K, int N) {
+  return gemv_persist_scratch_bytes(M, K, N);
+}
+
+extern "C" int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_f16, float eps, const int32_t *qweight,
+                                      const void *scales, void *out, int epilogue, int M, int K, int N, int group,
+                                      void *workspace, size_t workspace_bytes, void *stream) {
+  clear_error();
+  if (int rc = check_gemv_args(x, qweight, scales, out, M, K, N, group)) return rc;
+  AB200_REQUIRE(prologue >= 0 && prologue <= 2 && epilogue >= 0 && epilogue <= 2, "w4a16_gemv_fused: bad prologue %d / epilogue %d", prologue, epilogue);
+  AB200_REQUIRE(prologue != PRO_RMSNORM || norm_weight_f16 != nullptr, "w4a16_gemv_fused: RMSNorm prologue needs a weight vector");
+  AB200_REQUIRE(workspace == nullptr || (aligned16(workspace) && workspace_bytes >= gemv_persist_scratch_bytes(M, K, N)),
+                "w4a16_gemv_fused: workspace must be 16-byte aligned and hold %zu bytes", gemv_persist_scratch_bytes(M, K, N));
+  return gemv_f16(x, prologue, reinterpret_cast<const __half *>(norm_weight_f16), eps, qweight, scales, out, M, K, N, group, epilogue,
+                  workspace, (cudaStream_t)stream);
 }
 
 extern "C" int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream) {

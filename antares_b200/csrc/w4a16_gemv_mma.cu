@@ -285,12 +285,7 @@ static int launch_mma(Kern kern, MmaGemvParams p, int depth, cudaStream_t stream
   return AB200_OK;
 }
 
-// Auto: batches of 1-2 rows run on the scalar pipes (fewer instructions per CTA at that size),
-// larger batches on the warp MMA.
-bool gemv_mma_eligible(int dtype, int M) {
-  if (dtype != AB200_F16 || g_tune.impl == 1) return false;
-  return g_tune.impl == 2 || M > 2;
-}
+bool gemv_mma_eligible(int dtype, int M) { return dtype == AB200_F16 && g_tune.impl != 1; }
 
 template <int MB, int EPI>
 static int mma_by_group(const MmaGemvParams &p, cudaStream_t s) {
@@ -326,11 +321,13 @@ int gemv_tuning_set(const char *name, int value) {
   if (!strcmp(name, "gemv_cluster")) {
     if (!(value == 0 || value == 1 || value == 2 || value == 4 || value == 8)) return fail(AB200_EINVAL, "gemv_cluster must be 0, 1, 2, 4 or 8");
     g_tune.cluster = value;
+  } else if (!strcmp(name, "pdl")) {
+    pdl_set(value != 0);
   } else if (!strcmp(name, "gemv_depth")) {
     if (value != 0 && (value < 2 || value > 6)) return fail(AB200_EINVAL, "gemv_depth must be 0 or 2..6");
     g_tune.depth = value;
   } else if (!strcmp(name, "gemv_impl")) {
-    if (value < 0 || value > 2) return fail(AB200_EINVAL, "gemv_impl must be 0 (auto), 1 (scalar pipes) or 2 (warp MMA)");
+    if (value < 0 || value > 3) return fail(AB200_EINVAL, "gemv_impl must be 0 (auto), 1 (scalar pipes), 2 (cluster warp MMA) or 3 (persistent warp MMA)");
     g_tune.impl = value;
   } else {
     return fail(AB200_EINVAL, "unknown option %s", name);
@@ -339,5 +336,6 @@ int gemv_tuning_set(const char *name, int value) {
 }
 
 int gemv_tuning_cluster() { return g_tune.cluster; }
+int gemv_tuning_impl() { return g_tune.impl; }
 
 }  // namespace ab200

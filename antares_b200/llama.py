@@ -6,7 +6,8 @@ loop) with these B200-first differences:
     the generated ids live in device memory, so the loop needs no host round trip
     (the reference syncs on `int(torch.argmax(logits))` every token, line 200);
   * the residual stream is fp32, projection inputs/outputs fp16, KV cache fp16;
-  * RMSNorm computes its own sum of squares; residual adds are fused into the O/down GEMV;
+  * five launches per layer: RMSNorm is fused into the V|Q|K and gate|up projections, RoPE and the
+    cache update into the attention kernel, SiLU*up and the residual adds into the O/down projections;
   * tensor parallel over `world` GPUs: column-parallel V|Q|K and gate|up, row-parallel O and
     down with one all-reduce each, vocabulary-parallel classifier with an all-gather.
 Weights are seeded synthetic stand-ins for the GPTQ checkpoint (same shapes and value ranges).
@@ -155,26 +156,23 @@ class LlamaInt4Decoder:
         self._pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     # -- one decode step, eager (enqueues every kernel on the current stream) --------------------
-    def _gemv(self, x, q, s, out):
+    def _proj(self, x, q, s, out, prologue=0, epilogue=0, norm_w=None):
+        """One fused W4A16 projection launch (prologue 0 plain / 1 RMSNorm of the fp32 residual /
+        2 SiLU(gate)*up; epilogue 0 fp16 / 1 residual += / 2 fp32 partial)."""
         K, N = q.shape[0] * 8, q.shape[1]
-        call("ab200_w4a16_gemv", x.data_ptr(), q.data_ptr(), s.data_ptr(), out.data_ptr(), 1, K, N, self.cfg.group, 0, self._st)
+        call("ab200_w4a16_gemv_fused", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
+             q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, 0, 0, self._st)
         self._n += 1
 
-    def _gemv_out_proj(self, x, q, s):
+    def _row_parallel(self, x, q, s, prologue):
         """Row-parallel projection + residual: fused when alone, all-reduce of fp32 partials otherwise."""
-        K, N = q.shape[0] * 8, q.shape[1]
         if self.world == 1:
-            call("ab200_w4a16_gemv_residual", x.data_ptr(), q.data_ptr(), s.data_ptr(), self.x.data_ptr(), 1, K, N, self.cfg.group, self._st)
-            self._n += 1
+            self._proj(x, q, s, self.x, prologue, 1)
         else:
-            call("ab200_w4a16_gemv_f32out", x.data_ptr(), q.data_ptr(), s.data_ptr(), self.partial.data_ptr(), 1, K, N, self.cfg.group, self._st)
+            self._proj(x, q, s, self.partial, prologue, 2)
             self.comm.all_reduce_sum_(self.partial)
-            call("ab200_residual_add", self.x.data_ptr(), self.partial.data_ptr(), N, self._st)
-            self._n += 3
-
-    def _rmsnorm(self, weight):
-        call("ab200_rmsnorm", self.x.data_ptr(), 1, weight.data_ptr(), self.xb.data_ptr(), 1, self.cfg.dim, self.cfg.eps, self._st)
-        self._n += 1
+            call("ab200_residual_add", self.x.data_ptr(), self.partial.data_ptr(), self.cfg.dim, self._st)
+            self._n += 1
 
     def step_eager(self):
         cfg = self.cfg
@@ -184,25 +182,19 @@ class LlamaInt4Decoder:
         call("ab200_embed_lookup", self.embed.data_ptr(), self.token.data_ptr(), self.x.data_ptr(), cfg.dim, cfg.vocab, st)
         self._n += 1
         for l, w in enumerate(self.layers):
-            self._rmsnorm(w["att_norm"])
-            self._gemv(self.xb, w["vqk_q"], w["vqk_s"], self.vqk)
-            call("ab200_rope_kv_store", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), self.q.data_ptr(),
-                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.hl, cfg.head_dim, self.dl, cfg.max_seq, st)
-            call("ab200_attention_decode", self.q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(),
-                 self.att.data_ptr(), self.pos.data_ptr(), 1, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
-            self._n += 2
-            self._gemv_out_proj(self.att, w["o_q"], w["o_s"])
-            self._rmsnorm(w["ffn_norm"])
-            self._gemv(self.xb, w["gu_q"], w["gu_s"], self.gu)
-            call("ab200_silu_mul", self.gu.data_ptr(), self.h.data_ptr(), self.fl, st)
+            self._proj(self.x, w["vqk_q"], w["vqk_s"], self.vqk, 1, 0, w["att_norm"])        # RMSNorm + V|Q|K
+            call("ab200_attention_fused", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(),
+                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.att.data_ptr(), self.hl, cfg.head_dim,
+                 self.dl, cfg.max_seq, self.att_scale, st)                                  # RoPE + cache + attention
             self._n += 1
-            self._gemv_out_proj(self.h, w["down_q"], w["down_s"])
-        self._rmsnorm(self.final_norm)
+            self._row_parallel(self.att, w["o_q"], w["o_s"], 0)                               # O + residual
+            self._proj(self.x, w["gu_q"], w["gu_s"], self.gu, 1, 0, w["ffn_norm"])           # RMSNorm + gate|up
+            self._row_parallel(self.gu, w["down_q"], w["down_s"], 2)                          # SiLU*up + down + residual
+        call("ab200_rmsnorm", self.x.data_ptr(), 1, self.final_norm.data_ptr(), self.xb.data_ptr(), 1, cfg.dim, cfg.eps, st)
         call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), cfg.dim, self.vl, st)
-        self._n += 1
+        self._n += 2
         if self.world > 1:
             self.comm.all_gather_into(self.logits, self.logits_local)
-            self._n += 1
         call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), self._n_prompt_capture,
              self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), st)
         self._n += 1

@@ -189,3 +189,33 @@ def kernel_status():
     v = ctypes.c_int(0)
     call("ab200_kernel_status", ctypes.cast(ctypes.pointer(v), ctypes.c_void_p))
     return v.value
+
+
+PRO_PLAIN, PRO_RMSNORM, PRO_SILU_MUL = 0, 1, 2
+EPI_F16, EPI_RESIDUAL, EPI_F32 = 0, 1, 2
+
+
+def gemv_workspace_bytes(M, K, N):
+    return int(_lib.load().ab200_w4a16_gemv_workspace_bytes(int(M), int(K), int(N)))
+
+
+def w4a16_gemv_fused(x, qweight, scales, out, prologue=PRO_PLAIN, epilogue=EPI_F16, norm_weight=None, eps=1e-6,
+                     group=None, workspace=None):
+    """One-launch decode projection: optional RMSNorm / SiLU*up on the way in, optional residual
+    add on the way out.  x: fp16 [M,K] (plain), fp32 [M,K] (RMSNorm) or fp16 [M,2K] (SiLU*up)."""
+    Kp, N = qweight.shape
+    K = Kp * 8
+    xk = 2 * K if prologue == PRO_SILU_MUL else K
+    M = x.numel() // xk
+    if group is None:
+        group = K // scales.shape[0]
+    want_x = torch.float32 if prologue == PRO_RMSNORM else torch.float16
+    want_o = torch.float16 if epilogue == EPI_F16 else torch.float32
+    if out.numel() != M * N:
+        raise ValueError("out must hold %d elements" % (M * N))
+    ws_ptr, ws_bytes = (0, 0) if workspace is None else (_chk(workspace, "workspace"), workspace.numel() * workspace.element_size())
+    call("ab200_w4a16_gemv_fused", _chk(x, "x", want_x), int(prologue),
+         0 if norm_weight is None else _chk(norm_weight, "norm_weight", torch.float16), float(eps),
+         _chk(qweight, "qweight", torch.int32), _chk(scales, "scales", torch.float16), _chk(out, "out", want_o), int(epilogue),
+         M, K, N, group, ws_ptr, ws_bytes, _stream())
+    return out

@@ -217,10 +217,14 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
         n_launch, alg = 0, 0
         st = torch.cuda.current_stream().cuda_stream
         for w in dec.layers:
-            for x, q, s, out in ((dec.xb, w["vqk_q"], w["vqk_s"], dec.vqk), (dec.att, w["o_q"], w["o_s"], dec.xb),
-                                 (dec.xb, w["gu_q"], w["gu_s"], dec.gu), (dec.h, w["down_q"], w["down_s"], dec.xb)):
+            # the step's four projections with their fused prologues/epilogues (scratch buffers as outputs)
+            for x, q, s, out, pro, epi, nw in ((dec.x, w["vqk_q"], w["vqk_s"], dec.vqk, 1, 0, w["att_norm"]),
+                                               (dec.att, w["o_q"], w["o_s"], dec.partial, 0, 2, None),
+                                               (dec.x, w["gu_q"], w["gu_s"], dec.gu, 1, 0, w["ffn_norm"]),
+                                               (dec.gu, w["down_q"], w["down_s"], dec.partial, 2, 2, None)):
                 K, N = q.shape[0] * 8, q.shape[1]
-                call("ab200_w4a16_gemv", x.data_ptr(), q.data_ptr(), s.data_ptr(), out.data_ptr(), 1, K, N, cfg.group, 0, st)
+                call("ab200_w4a16_gemv_fused", x.data_ptr(), pro, 0 if nw is None else nw.data_ptr(), cfg.eps, q.data_ptr(),
+                     s.data_ptr(), out.data_ptr(), epi, 1, K, N, cfg.group, 0, 0, st)
                 n_launch += 1
                 alg += K * N // 2 + (K // cfg.group) * N * 2 + K * 2 + N * 2
 

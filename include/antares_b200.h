@@ -48,8 +48,10 @@ int ab200_kernel_status(int *status_host);
 
 /* Tuning knobs, the counterpart of the `config=` hints of autort.export
  * (samples/05_llama2_7b_int4.py:139).  Names: "gemv_cluster" (0 = auto, 1/2/4/8 K-slices per
- * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 warp MMA), "gemv_depth" (0 auto, 2..6 units of
- * prefetch per warp in the warp-MMA kernel).  Process-wide; host call. */
+ * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA),
+ * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel).
+ * "pdl" (0/1): launch kernels with programmatic dependent launch so that a kernel's weight
+ * prefetch overlaps the tail of its predecessor in the stream.  Process-wide; host call. */
 int ab200_set_option(const char *name, int value);
 
 /* Device property probe; replaces engine/cuda_properties.cc:35-52 (which prints
@@ -97,6 +99,24 @@ int ab200_w4a16_gemv_residual(const void *x, const int32_t *qweight, const void 
  * (Tensor-parallel decode has no counterpart in the reference: its samples are single-device.) */
 int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, const void *scales,
                             float *out_f32, int M, int K, int N, int group, void *stream);
+
+/* The decode step's fused form of the same contraction (fp16 weights path), one launch:
+ *   prologue  0: x is fp16 [M, K]
+ *             1: x is the fp32 residual stream [M, K]; the kernel applies RMSNorm with
+ *                norm_weight_f16 [K] and eps (replaces rmsnorm + matmul_dequat, lines 150-152,169-171)
+ *             2: x is fp16 [M, 2K] = gate | up; the kernel feeds silu(gate) * up (lines 171-172)
+ *   epilogue  0: out fp16 [M, N];  1: out fp32 [M, N] += fp16_round(result);  2: out fp32 [M, N]
+ * workspace: device scratch of at least ab200_w4a16_gemv_workspace_bytes(M, K, N) bytes, 16-byte
+ * aligned, whose first 64 KiB are zero before the first use (the kernel leaves them zero); NULL =
+ * use the library's own per-device scratch.  Calls sharing a workspace must not overlap on the
+ * GPU.  The library scratch is allocated (cudaMalloc + a device synchronise) by the first call
+ * that needs it on a device, also from ab200_w4a16_gemv / _residual / _f32out: make that first
+ * call outside stream capture. */
+int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_f16, float eps,
+                           const int32_t *qweight, const void *scales, void *out, int epilogue,
+                           int M, int K, int N, int group, void *workspace, size_t workspace_bytes,
+                           void *stream);
+size_t ab200_w4a16_gemv_workspace_bytes(int M, int K, int N);
 
 /* x_f32[i] += fp16_round(partial_f32[i]) — the residual update of lines 168,173 applied to an
  * all-reduced partial. */
@@ -152,6 +172,13 @@ int ab200_embed_lookup(const void *embed_f16, const int32_t *token_dev, float *x
 int ab200_rope_kv_store(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev,
                         void *q_out_f16, void *k_cache_f16, void *v_cache_f16, int H, int D,
                         long kv_stride, int max_seq, void *stream);
+
+/* The three calls above in one launch: splits vqk (V | Q | K), rotates Q and K at position
+ * *pos_dev, stores K and V into cache row *pos_dev and attends over rows 0..*pos_dev (lines
+ * 151-165).  Heads are split over several CTAs that merge through distributed shared memory. */
+int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev,
+                          void *k_cache_f16, void *v_cache_f16, void *out_f16, int H, int D,
+                          long kv_stride, int max_seq, float scale, void *stream);
 
 /* out[i] = silu(gate_up[i]) * gate_up[n + i], fp32 math (line 171). */
 int ab200_silu_mul(const void *gate_up_f16, void *out_f16, int n, void *stream);

@@ -96,3 +96,30 @@ def test_attention_decode(cuda, S):
     ref = cport.attention_decode(q, kc, vc, S, scale)
     y = ops.attention_decode(_dev(q, cuda), _dev(kc, cuda), _dev(vc, cuda), torch.tensor([S], dtype=torch.int32, device=cuda), scale)
     assert _err(y.cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("pos", [0, 1, 5, 130, 383])
+@pytest.mark.parametrize("H", [32, 4])
+def test_attention_fused_matches_unfused_chain(cuda, pos, H):
+    """rope(q), rope(k) -> cache row pos, v -> cache row pos, attention over rows 0..pos, in one launch."""
+    from antares_b200._lib import call
+    rng = np.random.default_rng(pos + H)
+    D, max_seq = 128, 512
+    vqk = rng.standard_normal(3 * H * D).astype(np.float16)
+    kc = rng.standard_normal((max_seq, H * D)).astype(np.float16)
+    vc = rng.standard_normal((max_seq, H * D)).astype(np.float16)
+    inv_freq = cport.make_inv_freq(D)
+    p = np.array([pos], np.int32)
+    q_r = cport.rope(vqk[H * D:2 * H * D].reshape(1, H, D), p, inv_freq)[0]
+    kc_ref, vc_ref = kc.copy(), vc.copy()
+    kc_ref[pos] = cport.rope(vqk[2 * H * D:].reshape(1, H, D), p, inv_freq).reshape(-1)
+    vc_ref[pos] = vqk[:H * D]
+    ref = cport.attention_decode(q_r, kc_ref, vc_ref, pos + 1, 1 / np.sqrt(D))
+    kc_d, vc_d = _dev(kc, cuda), _dev(vc, cuda)
+    out = torch.empty((H, D), dtype=torch.float16, device=cuda)
+    vqk_d, invf_d, pos_d = _dev(vqk, cuda), _dev(inv_freq, cuda), torch.tensor([pos], dtype=torch.int32, device=cuda)
+    call("ab200_attention_fused", vqk_d.data_ptr(), invf_d.data_ptr(), pos_d.data_ptr(), kc_d.data_ptr(), vc_d.data_ptr(), out.data_ptr(),
+         H, D, H * D, max_seq, 1 / np.sqrt(D), torch.cuda.current_stream().cuda_stream)
+    assert _err(out.cpu().numpy(), ref) <= TOL
+    assert _err(kc_d[pos].cpu().numpy(), kc_ref[pos]) <= TOL and torch.equal(vc_d[pos].cpu(), torch.from_numpy(vc_ref[pos]))
+    assert torch.equal(kc_d[pos + 1:].cpu(), torch.from_numpy(kc[pos + 1:])), "rows beyond pos must be untouched"

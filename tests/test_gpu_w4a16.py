@@ -137,3 +137,48 @@ def test_errors_are_raised_not_fallen_back(cuda):
         ops.w4a16_gemv(_dev(x, cuda)[:, :128], _dev(qw, cuda), _dev(sc, cuda))
     with pytest.raises(_lib.Ab200Error):
         ops.w4a16_gemv(_dev(packing.synth_x(17, 256, 2), cuda), _dev(qw, cuda), _dev(sc, cuda))
+
+
+@pytest.mark.parametrize("impl", [1, 2, 3])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (3, 11008, 4096), (1, 4096, 22016), (9, 1408, 2752), (2, 256, 36)])
+def test_every_gemv_variant_matches_oracle(cuda, impl, M, K, N):
+    """The scalar-pipe, cluster warp-MMA and persistent warp-MMA kernels compute the same contraction."""
+    qw, sc = packing.synth_w4(K, N, 31)
+    x = packing.synth_x(M, K, 32)
+    ref = cport.w4a16_gemm(x, qw, sc)
+    ops.set_option("gemv_impl", impl)
+    try:
+        y = ops.w4a16_gemv(_dev(x, cuda), _dev(qw, cuda), _dev(sc, cuda)).cpu().numpy()
+        y2 = ops.w4a16_gemv(_dev(x, cuda), _dev(qw, cuda), _dev(sc, cuda)).cpu().numpy()
+    finally:
+        ops.set_option("gemv_impl", 0)
+    assert _err(y, ref) <= TOL
+    assert np.array_equal(y.view(np.uint16), y2.view(np.uint16)), "results must be bitwise repeatable"
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_fused_rmsnorm_prologue_and_residual_epilogue(cuda, M):
+    K, N = 4096, 12288
+    qw, sc = packing.synth_w4(K, N, 41)
+    rng = np.random.default_rng(42)
+    x32 = (rng.standard_normal((M, K)) * 5).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    ref = cport.w4a16_gemm(cport.rmsnorm(x32, wn, 1e-6), qw, sc)
+    out = torch.empty((M, N), dtype=torch.float16, device=cuda)
+    ws = torch.zeros(ops.gemv_workspace_bytes(M, K, N), dtype=torch.uint8, device=cuda)
+    ops.w4a16_gemv_fused(_dev(x32, cuda), _dev(qw, cuda), _dev(sc, cuda), out, prologue=ops.PRO_RMSNORM,
+                         norm_weight=_dev(wn, cuda), eps=1e-6, workspace=ws)
+    assert _err(out.cpu().numpy(), ref) <= TOL
+    assert torch.count_nonzero(ws[:65536]) == 0, "tile counters must be left at zero"
+    # residual epilogue on a K=11008 projection with SiLU*up on the way in (x must fit shared memory
+    # next to the prefetch rings: up to 2 batch rows at this K)
+    M = min(M, 2)
+    K2, N2 = 11008, 4096
+    qw2, sc2 = packing.synth_w4(K2, N2, 43)
+    gu = rng.standard_normal((M, 2 * K2)).astype(np.float16)
+    h = np.stack([cport.silu_mul(gu[m, :K2].copy(), gu[m, K2:].copy()) for m in range(M)])
+    resid0 = rng.standard_normal((M, N2)).astype(np.float32)
+    ref2 = resid0 + cport.w4a16_gemm(h, qw2, sc2).astype(np.float32)
+    resid = _dev(resid0, cuda)
+    ops.w4a16_gemv_fused(_dev(gu, cuda), _dev(qw2, cuda), _dev(sc2, cuda), resid, prologue=ops.PRO_SILU_MUL, epilogue=ops.EPI_RESIDUAL)
+    assert _err(resid.cpu().numpy(), ref2) <= TOL
