@@ -10,8 +10,8 @@
 //   scales fp16/fp32 [K/group, N]; x [M, K]; out [M, N].
 //
 // Decomposition: CTA = 128 columns x a contiguous slice of K; its 8 warps take 32-k "units"
-// (4 packed rows) round-robin, with the next unit's 4 loads in flight while the current one is
-// multiplied.  The K slices of one column tile are the CTAs of one thread-block cluster; the
+// (4 packed rows) round-robin, with two units' loads (8 x 16 B per thread) in flight, the first
+// ones issued before x is staged.  The K slices of one column tile are the CTAs of one thread-block cluster; the
 // partial sums meet in distributed shared memory in a fixed order (deterministic, no global
 // scratch, no atomics).  HBM-bound: algorithmic bytes = K*N/2 + (K/group)*N*2 + M*K*2 + M*N*2.
 //
@@ -66,8 +66,9 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   const int32_t *qcol = p.qw + n0;
   const __half *scol = reinterpret_cast<const __half *>(p.scales) + n0;
 
-  uint4 wbuf[2][UNIT_ROWS];
-  uint2 sbuf[2];
+  constexpr int NBUF = 2;  // units in flight per warp (registers)
+  uint4 wbuf[NBUF][UNIT_ROWS];
+  uint2 sbuf[NBUF];
   auto load_unit = [&](int u, int b) {
     if (col_ok) {
       const int32_t *q = qcol + (size_t)u * UNIT_ROWS * p.N;
@@ -83,7 +84,10 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 
   pdl_launch_dependents();
   int u = u_begin + warp;
-  if (u < u_end) load_unit(u, 0);  // weights are on their way before x is staged
+  // the first NBUF units of this warp are on their way before x is staged
+#pragma unroll
+  for (int b = 0; b < NBUF; ++b)
+    if (u + b * GEMV_WARPS < u_end) load_unit(u + b * GEMV_WARPS, b);
   pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
@@ -197,16 +201,16 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
       }
   };
 
-  // Two-deep software pipeline over this warp's units.
+  // NBUF-deep software pipeline over this warp's units: a buffer is refilled as soon as it is consumed.
   while (u < u_end) {
-    const int u1 = u + GEMV_WARPS;
-    if (u1 < u_end) load_unit(u1, 1);
-    compute_unit(u, 0);
-    if (u1 >= u_end) break;
-    const int u2 = u1 + GEMV_WARPS;
-    if (u2 < u_end) load_unit(u2, 0);
-    compute_unit(u1, 1);
-    u = u2;
+#pragma unroll
+    for (int b = 0; b < NBUF; ++b) {
+      if (u < u_end) {
+        compute_unit(u, b);
+        if (u + NBUF * GEMV_WARPS < u_end) load_unit(u + NBUF * GEMV_WARPS, b);
+      }
+      u += GEMV_WARPS;
+    }
   }
 
   reduce_and_store<M, EPI, GEMV_THREADS, GEMV_WARPS>(facc, red, part, p.out, p.N, tile * TILE_N);
@@ -385,24 +389,22 @@ static int gemv_f16_scalar(GemvParams p, int M, int epi, cudaStream_t s) {
   return gemv_f16_direct<EPI_STORE_F32, PRO>(p, M, s);
 }
 
-// fp16 path.  Auto choice: batches of 1-2 rows on the scalar-pipe cluster kernel (lowest fixed
-// cost and best streaming rate at that size), 3-16 rows on the persistent warp-MMA kernel (needs
-// scratch; scratch == nullptr means the library-owned buffer), cluster warp-MMA when x does not
-// fit the persistent kernel's shared memory.
+// fp16 path.  Auto choice (measured on B200): batches of 1-2 rows on the scalar-pipe cluster kernel
+// (lowest fixed cost and best streaming rate at that size), 3-16 rows on the cluster warp-MMA
+// kernel (constant cost in the batch size).  The persistent warp-MMA kernel (option gemv_impl=3)
+// needs scratch; scratch == nullptr means the library-owned buffer.
 static int gemv_f16(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
                     int K, int N, int group, int epi, void *scratch, cudaStream_t s) {
   const int impl = gemv_tuning_impl();
   const bool persist_ok = gemv_persist_fits(M, K, N) && N % 4 == 0;
-  if ((impl == 3 || (impl == 0 && M > 2)) && persist_ok) {
+  if (impl == 3 && persist_ok) {
     if (!scratch) {
       if (int rc = library_scratch(gemv_persist_scratch_bytes(M, K, N), &scratch)) return rc;
     }
     return gemv_persist_dispatch(x, norm_w, eps, qw, scales, out, M, K, N, group, pro, epi, scratch, s);
   }
-  if (impl == 2 || (impl == 0 && M > 2)) {
-    if (pro != PRO_PLAIN) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: fused prologue with M=%d K=%d does not fit the warp-MMA kernels", M, K);
-    return gemv_mma_dispatch(x, qw, scales, out, M, K, N, group, epi, s);
-  }
+  if ((impl == 2 || (impl == 0 && M > 2)) && gemv_mma_eligible(AB200_F16, M, K, N))
+    return gemv_mma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s);
   GemvParams p{x, qw, scales, out, K, N, group, K / UNIT_K, 0};
   p.norm_w = norm_w;
   p.eps = eps;

@@ -48,49 +48,6 @@ struct PersistParams {
   float eps;
 };
 
-__device__ __forceinline__ void mma16816p(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ float4 ldcg_f4(const float *p) {
-  float4 v;
-  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
-}
-
-__device__ __forceinline__ uint4 permute_row(uint4 v) {  // (x0..x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7)
-  uint4 o;
-  o.x = __byte_perm(v.x, v.z, 0x5410);
-  o.y = __byte_perm(v.x, v.z, 0x7632);
-  o.z = __byte_perm(v.y, v.w, 0x5410);
-  o.w = __byte_perm(v.y, v.w, 0x7632);
-  return o;
-}
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-// A-operand quad for two MMAs from two packed words (columns c and c+1 of this thread):
-// lo = {(k0,k4) of w0, (k0,k4) of w1, (k1,k5) of w0, (k1,k5) of w1}, hi = same for (k2,k6)/(k3,k7).
-__device__ __forceinline__ void unpack_pair(uint32_t w0, uint32_t w1, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
-  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
-  const __half2 c1032 = u2h2(0x64086408u), c16th = u2h2(0x2C002C00u), cm72 = u2h2(0xD480D480u);
-  const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
-  lo[0] = h22u(__hsub2(u2h2(lop3<0xEA>(w0, LO, MAGIC)), c1032));
-  lo[1] = h22u(__hsub2(u2h2(lop3<0xEA>(w1, LO, MAGIC)), c1032));
-  lo[2] = h22u(__hfma2(u2h2(lop3<0xEA>(w0, HI, MAGIC)), c16th, cm72));
-  lo[3] = h22u(__hfma2(u2h2(lop3<0xEA>(w1, HI, MAGIC)), c16th, cm72));
-  hi[0] = h22u(__hsub2(u2h2(lop3<0xEA>(w0s, LO, MAGIC)), c1032));
-  hi[1] = h22u(__hsub2(u2h2(lop3<0xEA>(w1s, LO, MAGIC)), c1032));
-  hi[2] = h22u(__hfma2(u2h2(lop3<0xEA>(w0s, HI, MAGIC)), c16th, cm72));
-  hi[3] = h22u(__hfma2(u2h2(lop3<0xEA>(w1s, HI, MAGIC)), c16th, cm72));
-}
-
 // MB = 8 or 16 batch rows; SPG = steps per scale group within a 128-k block (4, 2 or 1).
 // Requires K % 128 == 0 and N % 4 == 0.  All index arithmetic in the streaming loop is 32-bit
 // pointer bumping: no multiplies, no bounds predicates (out-of-range columns are clamped to the
