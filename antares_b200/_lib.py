@@ -37,9 +37,9 @@ SIGNATURES = {
     "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],
     "ab200_rmsnorm_vsum": [_vp, _vp, _vp, _vp, _sz, _f, _f, _i, _vp],
     "ab200_rmsnorm": [_vp, _i, _vp, _vp, _i, _i, _f, _vp],
-    "ab200_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "ab200_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ab200_softmax": [_vp, _vp, _i, _i, _i, _vp],
-    "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],
+    "ab200_attention_decode": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _i, _vp],
     "ab200_embed_lookup": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_rope_kv_store": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _vp],
     "ab200_attention_fused": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp],

@@ -1,0 +1,137 @@
+"""The AutoRT calling surface, kept so that scripts written for the reference run on the B200
+kernel library unchanged.
+
+Reference usage (the AutoRT package itself ships only as a wheel; call sites are in-tree):
+  f = autort.export(ir=..., inputs=["name=dtype[Dim:val, ...]"], config=..., name=...)   README.md:63-69
+  f(x, qweight, scales, out=buf)            samples/05_llama2_7b_int4.py:135-144
+  autort.ops.rmsnorm_f32(x, vsum, w, extra=[1/N])                  samples/05_llama2_7b_int4.py:128-131
+  autort.ops.rotary_f32(x.view(H,2,-1), inv_freq, out, extra=[pos])  samples/05_llama2_7b_int4.py:157-158
+  autort.ops.attention_f32(q, k, v, att_f)                           samples/05_llama2_7b_int4.py:161-165
+  autort.device()                                                    samples/05_llama2_7b_int4.py:78
+
+Calling convention kept: tensors positionally in declared order; the result is returned, or
+written into a trailing positional tensor / `out=`; scalars come through `extra=[...]`; dimensions
+declared `Name:val` are upper bounds, the call may pass fewer elements (README.md:64-67).
+`config=` carries tuner hints in the reference ("tune:5", "~N~:[256,8,32],..."): the kernels here
+are hand-scheduled, so it is accepted and ignored.  IR outside the built operator family raises
+NotImplementedError; nothing runs on the CPU.
+"""
+import torch
+
+from . import ir as _ir
+from . import ops as _ops
+
+RMS_EPS = 1e-6  # epsilon of the built-in rmsnorm ops (the reference's value is inside its closed wheel)
+
+_TORCH_DT = {"float16": torch.float16, "float32": torch.float32, "int32": torch.int32}
+
+
+def device():
+    """The device custom ops run on (samples/05_llama2_7b_int4.py:78)."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("antares_b200 needs a CUDA device: there is no CPU backend")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+class _OpNamespace:
+    """autort.ops.<name>: ops registered by export() plus the built-in Llama ops."""
+
+    def _register(self, name, fn):
+        setattr(self, name, fn)
+
+
+ops = _OpNamespace()
+
+
+def _split_call(match, tensors, out):
+    """Positional tensors = declared inputs [+ output].  Returns (inputs by name, out)."""
+    n_in = len(match.inputs)
+    if len(tensors) == n_in + 1 and out is None:
+        tensors, out = tensors[:n_in], tensors[n_in]
+    if len(tensors) != n_in:
+        raise TypeError("%s expects %d tensors (%s)%s, got %d" % (match.name, n_in, ", ".join(s.name for s in match.inputs),
+                                                                  " plus an optional output", len(tensors)))
+    by_name = {}
+    for spec, t in zip(match.inputs, tensors):
+        want = _TORCH_DT.get(spec.dtype)
+        if want is not None and t.dtype != want:
+            raise TypeError("%s: tensor %s must be %s, got %s" % (match.name, spec.name, spec.dtype, t.dtype))
+        if t.dim() != len(spec.dims):
+            raise ValueError("%s: tensor %s must have %d dimensions" % (match.name, spec.name, len(spec.dims)))
+        for size, bound, dyn in zip(t.shape, spec.dims, spec.dyn):
+            if (dyn is None and size != bound) or size > bound:
+                raise ValueError("%s: tensor %s has extent %d where %s%d is declared" % (match.name, spec.name, size, "at most " if dyn else "", bound))
+        by_name[spec.name] = t.contiguous()
+    return by_name, out
+
+
+def export(ir, inputs, config=None, name=None):
+    """Binds an Antares-IR program to its hand-written kernel and registers it as autort.ops.<name>."""
+    match = _ir.recognise(ir, inputs, name)
+    if match.kind == "w4a16":
+        pr = match.params
+
+        def fn(*tensors, out=None, extra=None):
+            t, out = _split_call(match, tensors, out)
+            x, qw, sc = t[pr["x"]], t[pr["qweight"]], t[pr["scales"]]
+            res = _ops.w4a16_matmul(x, qw, sc, out=out, group=pr["group"])
+            return res
+    elif match.kind == "sigmoid":
+        def fn(*tensors, out=None, extra=None):
+            t, out = _split_call(match, tensors, out)
+            return _ops.sigmoid(t[match.params["x"]], out=out)
+    elif match.kind == "softmax":
+        def fn(*tensors, out=None, extra=None):
+            t, out = _split_call(match, tensors, out)
+            return _ops.softmax(t[match.params["x"]], out=out)
+    else:  # pragma: no cover - recognise() raises first
+        raise NotImplementedError(match.kind)
+    fn.__name__ = match.name
+    fn.match = match
+    ops._register(match.name, fn)
+    return fn
+
+
+# ---- built-in ops of the Llama samples (closed in the reference; definitions in the oracle) ----------
+
+def _rmsnorm(dtype):
+    def fn(x, vsum, weight, out=None, extra=None):
+        if not extra:
+            raise TypeError("rmsnorm needs extra=[1/N]")
+        if x.dtype != dtype or weight.dtype != dtype:
+            raise TypeError("rmsnorm_%s: x and weight must be %s" % ("f32" if dtype == torch.float32 else "f16", dtype))
+        return _ops.rmsnorm_vsum(x.contiguous(), vsum.reshape(1).float(), weight.contiguous(), float(extra[0]), RMS_EPS, out=out)
+    return fn
+
+
+def _rotary(dtype):
+    def fn(x, inv_freq, out=None, extra=None):
+        if not extra:
+            raise TypeError("rotary needs extra=[pos]")
+        if x.dtype != dtype:
+            raise TypeError("rotary: x must be %s" % dtype)
+        H = x.shape[0]
+        D = x.numel() // H                      # x arrives as [H, 2, D/2]: the same memory as [H, D]
+        pos = torch.tensor([int(extra[0])], dtype=torch.int32, device=x.device)
+        res = _ops.rope(x.contiguous().view(1, H, D), pos, inv_freq.float().contiguous(),
+                        out=None if out is None else out.view(1, H, D))
+        return res.view(H, D) if out is None else out
+    return fn
+
+
+def _attention(dtype):
+    def fn(q, k, v, att_f, out=None, extra=None):
+        if q.dtype != dtype:
+            raise TypeError("attention: q must be %s" % dtype)
+        H, D = q.shape
+        S = k.shape[0]                           # caches arrive narrowed to the rows to attend (line 162)
+        seq = torch.tensor([S], dtype=torch.int32, device=q.device)
+        return _ops.attention_decode(q.contiguous(), k, v, seq, float(att_f.reshape(-1)[0]), out=out,
+                                     kv_stride=k.stride(0), max_seq=S)
+    return fn
+
+
+for _suffix, _dt in (("f32", torch.float32), ("f16", torch.float16)):
+    ops._register("rmsnorm_" + _suffix, _rmsnorm(_dt))
+    ops._register("rotary_" + _suffix, _rotary(_dt))
+    ops._register("attention_" + _suffix, _attention(_dt))

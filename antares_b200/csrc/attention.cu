@@ -11,6 +11,18 @@ namespace ab200 {
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_D = 128;
 
+// 8 consecutive elements as fp32, from fp16 or fp32 storage (streaming loads)
+template <typename T>
+__device__ __forceinline__ void ld8(const T *p, float (&f)[8]);
+__device__ __forceinline__ void h8_to_f8(const uint4 v, float (&f)[8]);
+template <>
+__device__ __forceinline__ void ld8<__half>(const __half *p, float (&f)[8]) { h8_to_f8(ldg_stream_v4(p), f); }
+template <>
+__device__ __forceinline__ void ld8<float>(const float *p, float (&f)[8]) {
+  const uint4 a = ldg_stream_v4(p), b = ldg_stream_v4(p + 4);
+  f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+  f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+}
 __device__ __forceinline__ void h8_to_f8(const uint4 v, float (&f)[8]) {
   const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -25,8 +37,9 @@ __device__ __forceinline__ void h8_to_f8(const uint4 v, float (&f)[8]) {
 // samples/05_llama2_7b_int4.py:161-165): p = softmax_s(scale * q.K_s), out = sum_s p_s V_s.
 // Phase 1: a half-warp per cache row computes the score (16 lanes x 8 dims).
 // Phase 2: block-wide max / sum of exp.  Phase 3: 16 row-groups x 16 dim-chunks accumulate P.V.
-__global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __half *__restrict__ q, const __half *__restrict__ kc,
-                                                                      const __half *__restrict__ vc, __half *__restrict__ out,
+template <typename T>
+__global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *__restrict__ q, const T *__restrict__ kc,
+                                                                      const T *__restrict__ vc, T *__restrict__ out,
                                                                       const int32_t *__restrict__ seq_len_dev, int seq_len_add,
                                                                       int max_seq, long kv_stride, float scale) {
   extern __shared__ __align__(16) float att_smem[];
@@ -40,15 +53,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __h
   const int sub = lane & 15, hw = lane >> 4;
 
   float qf[8];
-  h8_to_f8(*reinterpret_cast<const uint4 *>(q + (size_t)h * ATT_D + sub * 8), qf);
-  const __half *kh = kc + (size_t)h * ATT_D + sub * 8;
+  ld8<T>(q + (size_t)h * ATT_D + sub * 8, qf);
+  const T *kh = kc + (size_t)h * ATT_D + sub * 8;
   float mx = -CUDART_INF_F;
   for (int s0 = warp * 2; s0 < S; s0 += 2 * (ATT_THREADS / 32)) {
     const int s = s0 + hw;
     float dot = 0.f;
     if (s < S) {
       float kf[8];
-      h8_to_f8(ldg_stream_v4(kh + (size_t)s * kv_stride), kf);
+      ld8<T>(kh + (size_t)s * kv_stride, kf);
 #pragma unroll
       for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
     }
@@ -81,10 +94,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __h
 
   const int dchunk = threadIdx.x & 15, sgroup = threadIdx.x >> 4;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  const __half *vh = vc + (size_t)h * ATT_D + dchunk * 8;
+  const T *vh = vc + (size_t)h * ATT_D + dchunk * 8;
   for (int s = sgroup; s < S; s += 16) {
     float vf[8];
-    h8_to_f8(ldg_stream_v4(vh + (size_t)s * kv_stride), vf);
+    ld8<T>(vh + (size_t)s * kv_stride, vf);
     const float ps = p[s];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps, vf[j], acc[j]);
@@ -96,7 +109,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const __h
     float t = 0.f;
 #pragma unroll
     for (int g = 0; g < 16; ++g) t += red[g * ATT_D + threadIdx.x];
-    out[(size_t)h * ATT_D + threadIdx.x] = __float2half_rn(S > 0 ? t / sum : 0.f);
+    out[(size_t)h * ATT_D + threadIdx.x] = (T)(S > 0 ? t / sum : 0.f);
   }
 }
 
@@ -298,7 +311,7 @@ using namespace ab200;
 
 extern "C" int ab200_attention_decode(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16,
                                       const int32_t *seq_len_dev, int seq_len_add, int max_seq, int H, int D, long kv_stride,
-                                      float scale, void *stream) {
+                                      float scale, int dtype, void *stream) {
   clear_error();
   AB200_REQUIRE(q_f16 && k_cache_f16 && v_cache_f16 && out_f16 && seq_len_dev, "attention_decode: null pointer");
   AB200_REQUIRE(D == ATT_D, "attention_decode: head size %d is not the built size %d", D, ATT_D);
@@ -307,11 +320,21 @@ extern "C" int ab200_attention_decode(const void *q_f16, const void *k_cache_f16
                 "attention_decode: pointers must be 16-byte aligned");
   const size_t smem = ((size_t)max_seq + 16 * ATT_D) * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_decode: max_seq=%d exceeds the shared-memory score buffer", max_seq);
-  if (smem > 48 * 1024)
-    AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-  attention_decode_kernel<<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const __half *)q_f16, (const __half *)k_cache_f16,
-                                                                         (const __half *)v_cache_f16, (__half *)out_f16, seq_len_dev,
-                                                                         seq_len_add, max_seq, kv_stride, scale);
+  if (dtype == AB200_F16) {
+    if (smem > 48 * 1024)
+      AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attention_decode_kernel<__half><<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const __half *)q_f16, (const __half *)k_cache_f16,
+                                                                                   (const __half *)v_cache_f16, (__half *)out_f16, seq_len_dev,
+                                                                                   seq_len_add, max_seq, kv_stride, scale);
+  } else if (dtype == AB200_F32) {
+    if (smem > 48 * 1024)
+      AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attention_decode_kernel<float><<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const float *)q_f16, (const float *)k_cache_f16,
+                                                                                  (const float *)v_cache_f16, (float *)out_f16, seq_len_dev,
+                                                                                  seq_len_add, max_seq, kv_stride, scale);
+  } else {
+    return fail(AB200_EINVAL, "attention_decode: unknown dtype %d", dtype);
+  }
   AB200_CHECK_LAUNCH("attention_decode");
   return AB200_OK;
 }

@@ -133,8 +133,9 @@ __global__ void rmsnorm_vsum_kernel(const T *__restrict__ x, const float *__rest
 // One CTA per row (= position).  A thread owns 8 consecutive j of the first half and their
 // partners in the second half; the angle depends on (row, j) only, so sin/cos are computed once
 // and reused over the heads the thread walks.
-__global__ void __launch_bounds__(ROW_THREADS) rope_kernel(const __half *__restrict__ x, const float *__restrict__ inv_freq,
-                                                          const int32_t *__restrict__ pos, __half *__restrict__ out,
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS) rope_kernel(const T *__restrict__ x, const float *__restrict__ inv_freq,
+                                                          const int32_t *__restrict__ pos, T *__restrict__ out,
                                                           int H, int D) {
   const size_t row = blockIdx.x;
   const int half = D / 2, chunks = half / 8;
@@ -147,15 +148,15 @@ __global__ void __launch_bounds__(ROW_THREADS) rope_kernel(const __half *__restr
   for (int h = hslot; h < H; h += hstep) {
     const size_t base = (row * H + h) * (size_t)D + jc * 8;
     float a[8], b[8], oa[8], ob[8];
-    load8<__half>(x + base, a);
-    load8<__half>(x + base + half, b);
+    load8<T>(x + base, a);
+    load8<T>(x + base + half, b);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       oa[j] = a[j] * c[j] - b[j] * s[j];
       ob[j] = b[j] * c[j] + a[j] * s[j];
     }
-    store8<__half>(out + base, oa);
-    store8<__half>(out + base + half, ob);
+    store8<T>(out + base, oa);
+    store8<T>(out + base + half, ob);
   }
 }
 
@@ -372,13 +373,15 @@ extern "C" int ab200_rmsnorm(const void *x, int x_dtype, const void *weight_f16,
 }
 
 extern "C" int ab200_rope(const void *x_f16, const float *inv_freq, const int32_t *pos, void *out_f16, int rows, int H,
-                          int D, void *stream) {
+                          int D, int dtype, void *stream) {
   clear_error();
   AB200_REQUIRE(x_f16 && inv_freq && pos && out_f16, "rope: null pointer");
   AB200_REQUIRE(D > 0 && D % 16 == 0 && D / 16 <= ROW_THREADS && H > 0 && rows >= 0, "rope: D=%d must be a multiple of 16 (at most %d), H=%d positive", D, ROW_THREADS * 16, H);
   AB200_REQUIRE(aligned16(x_f16) && aligned16(out_f16), "rope: pointers must be 16-byte aligned");
   if (rows == 0) return AB200_OK;
-  rope_kernel<<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)x_f16, inv_freq, pos, (__half *)out_f16, H, D);
+  if (dtype == AB200_F16) rope_kernel<__half><<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)x_f16, inv_freq, pos, (__half *)out_f16, H, D);
+  else if (dtype == AB200_F32) rope_kernel<float><<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const float *)x_f16, inv_freq, pos, (float *)out_f16, H, D);
+  else return fail(AB200_EINVAL, "rope: unknown dtype %d", dtype);
   AB200_CHECK_LAUNCH("rope");
   return AB200_OK;
 }

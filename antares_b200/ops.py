@@ -150,8 +150,8 @@ def rope(x, pos, inv_freq, out=None):
     rows, H, D = x.shape
     if out is None:
         out = torch.empty_like(x)
-    call("ab200_rope", _chk(x, "x", torch.float16), _chk(inv_freq, "inv_freq", torch.float32),
-         _chk(pos, "pos", torch.int32), _chk(out, "out", torch.float16), rows, H, D, _stream())
+    call("ab200_rope", _chk(x, "x"), _chk(inv_freq, "inv_freq", torch.float32),
+         _chk(pos, "pos", torch.int32), _chk(out, "out", x.dtype), rows, H, D, _code(x.dtype), _stream())
     return out
 
 
@@ -172,9 +172,11 @@ def attention_decode(q, k_cache, v_cache, seq_len_dev, scale, out=None, kv_strid
         max_seq = k_cache.shape[0]
     if out is None:
         out = torch.empty_like(q)
-    call("ab200_attention_decode", _chk(q, "q", torch.float16), k_cache.data_ptr(), v_cache.data_ptr(),
-         _chk(out, "out", torch.float16), _chk(seq_len_dev, "seq_len_dev", torch.int32), int(seq_len_add), int(max_seq), H, D,
-         int(kv_stride), float(scale), _stream())
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("q, k_cache and v_cache must share a dtype")
+    call("ab200_attention_decode", _chk(q, "q"), k_cache.data_ptr(), v_cache.data_ptr(),
+         _chk(out, "out", q.dtype), _chk(seq_len_dev, "seq_len_dev", torch.int32), int(seq_len_add), int(max_seq), H, D,
+         int(kv_stride), float(scale), _code(q.dtype), _stream())
     return out
 
 

@@ -144,21 +144,21 @@ int ab200_rmsnorm(const void *x, int x_dtype, const void *weight_f16, void *out_
                   int cols, float eps, void *stream);
 
 /* autort.ops.rotary_f32(x.view(H,2,D/2), inv_freq[D], out[H,D], extra=[pos]) — call site
- * samples/05_llama2_7b_int4.py:157-158, batched: x, out fp16 [rows, H, D]; row r is rotated by
+ * samples/05_llama2_7b_int4.py:157-158, batched: x, out [rows, H, D] in dtype; row r is rotated by
  * position pos[r] (int32 device array); inv_freq fp32 [D/2 or D]. Rotate-half convention. */
-int ab200_rope(const void *x_f16, const float *inv_freq, const int32_t *pos, void *out_f16,
-               int rows, int H, int D, void *stream);
+int ab200_rope(const void *x, const float *inv_freq, const int32_t *pos, void *out, int rows,
+               int H, int D, int dtype, void *stream);
 
 /* Row softmax — AntaresIR.md:226.  x, out [rows, cols] in dtype. */
 int ab200_softmax(const void *x, void *out, int rows, int cols, int dtype, void *stream);
 
 /* autort.ops.attention_f32(q[H,D], K[S,H,D], V[S,H,D], att_f[1]) — call site
- * samples/05_llama2_7b_int4.py:161-165.  fp16 q/K/V/out, fp32 math.  The number of cache rows
+ * samples/05_llama2_7b_int4.py:161-165.  q/K/V/out in dtype (F16 or F32), fp32 math.  The number of cache rows
  * attended is S = *seq_len_dev + seq_len_add (a device int, so a captured graph can be replayed as the
  * sequence grows); kv_stride = elements between consecutive cache rows; D == 128. */
-int ab200_attention_decode(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16,
-                           void *out_f16, const int32_t *seq_len_dev, int seq_len_add, int max_seq,
-                           int H, int D, long kv_stride, float scale, void *stream);
+int ab200_attention_decode(const void *q, const void *k_cache, const void *v_cache, void *out,
+                           const int32_t *seq_len_dev, int seq_len_add, int max_seq, int H, int D,
+                           long kv_stride, float scale, int dtype, void *stream);
 
 /* ---- decode-step glue (replaces torch eager ops in samples/05_llama2_7b_int4.py:146-177) -- */
 

@@ -1,0 +1,102 @@
+"""GPU tests of the drop-in surface: the call sites of the reference's samples, verbatim, against the
+CPU oracle.  Tolerance: max|err| <= 1e-2 * max|ref| (fp32 variants much tighter)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import autort
+from antares_b200 import packing
+from antares_b200.custom_op import CustomOp
+from oracle import cport
+
+pytestmark = pytest.mark.gpu
+
+W4A16_IR = """
+  input1[S, N] = (qweight[S / 8, N] >> (S % 8 * 4)).call(strs.bitwise_and, 15) * input0[S].like(1)
+  w[S, N] = scales[S / 128, N] * (input1[S, N] - 8)
+  my_result[N] +=! input0[S] * w[S, N].to(input0.dtype())
+"""
+
+
+def _err(y, ref):
+    y, ref = np.asarray(y, np.float32), np.asarray(ref, np.float32)
+    return np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+def test_export_w4a16_as_in_the_int4_sample(cuda):
+    """samples/05_llama2_7b_int4.py:135-144 with its own dtypes (fp32 x and scales), out= and dynamic dims."""
+    fn = autort.export(ir=W4A16_IR, inputs=["input0=float32[S:4096]", "qweight=int32[L:512, N:12288]", "scales=float32[K:32, N:12288]"],
+                       config="~N~:[256,8,32],~S~:[64,8]")
+    assert autort.ops.my_result is fn
+    for N in (12288, 4096):  # one exported op serves every projection (dims are upper bounds)
+        qw, sc = packing.synth_w4(4096, N, 3, scales_dtype=np.float32)
+        x = packing.synth_x(1, 4096, 4, np.float32)[0]
+        ref = cport.w4a16_gemm(x, qw, sc)
+        dev = autort.device()
+        out = torch.empty(N, dtype=torch.float32, device=dev)
+        res = fn(torch.from_numpy(x).to(dev), torch.from_numpy(qw).to(dev), torch.from_numpy(sc).to(dev), out=out.view(-1))
+        assert res.data_ptr() == out.data_ptr()
+        assert _err(out.cpu().numpy(), ref) <= 1e-4
+    with pytest.raises(ValueError):
+        fn(torch.zeros(8192, device=dev), torch.zeros(1024, 64, dtype=torch.int32, device=dev), torch.zeros(64, 64, device=dev))
+
+
+def test_export_sigmoid_as_in_the_readme(cuda):
+    data = torch.arange(0, 10, dtype=torch.float32, device=autort.device())
+    f = autort.export(ir="sigmoid_f32[N] = 1 - 1 / (1 + data[N].call(strs.exp))", inputs=["data=float32[N:4096000]"], config="tune:5")
+    want = [0.5000, 0.7311, 0.8808, 0.9526, 0.9820, 0.9933, 0.9975, 0.9991, 0.9997, 0.9999]  # README.md:67
+    assert np.allclose(f(data).cpu().numpy(), want, atol=1e-4)
+    assert np.allclose(autort.ops.sigmoid_f32(data).cpu().numpy(), want, atol=1e-4)
+
+
+def test_builtin_llama_ops_follow_the_sample_call_sites(cuda):
+    dev = autort.device()
+    rng = np.random.default_rng(0)
+    n_heads, head_size, dim, pos = 32, 128, 4096, 5
+    # rmsnorm (samples/05_llama2_7b_int4.py:128-131)
+    x = torch.from_numpy(rng.standard_normal(dim).astype(np.float32)).to(dev)
+    wgt = torch.from_numpy((1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)).to(dev)
+    vsum = (x * x).sum().view(1)
+    y = autort.ops.rmsnorm_f32(x.view(-1), vsum, wgt, extra=[1.0 / int(x.numel())])
+    ref = cport.rmsnorm_vsum_f32(x.cpu().numpy(), vsum.cpu().numpy(), wgt.cpu().numpy(), 1.0 / dim)
+    assert _err(y.cpu().numpy(), ref) <= 1e-5
+    # rotary (lines 125-126, 157-158)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, head_size, 2).float() / head_size)))
+    inv_freq = torch.cat([inv_freq, inv_freq]).view(head_size).to(dev)
+    sq = torch.from_numpy(rng.standard_normal(dim).astype(np.float32)).to(dev)
+    sq_out = torch.empty_like(sq).view(n_heads, head_size)
+    autort.ops.rotary_f32(sq.view(n_heads, 2, -1), inv_freq, sq_out, extra=[pos, ])
+    ref = cport.rope(sq.cpu().numpy().astype(np.float16).reshape(1, n_heads, head_size), np.array([pos], np.int32), inv_freq.cpu().numpy())
+    assert _err(sq_out.cpu().numpy(), ref[0]) <= 2e-3
+    # attention (lines 161-165): caches narrowed to pos + 1 rows
+    kc = torch.from_numpy(rng.standard_normal((256, dim)).astype(np.float16)).to(dev)
+    vc = torch.from_numpy(rng.standard_normal((256, dim)).astype(np.float16)).to(dev)
+    q = torch.from_numpy(rng.standard_normal((n_heads, head_size)).astype(np.float16)).to(dev)
+    att_f = torch.tensor([1 / math.sqrt(head_size)], dtype=torch.float32, device=dev)
+    b_sk = kc.view(256, n_heads, head_size).narrow(0, 0, pos + 1)
+    b_sv = vc.view(256, n_heads, head_size).narrow(0, 0, pos + 1)
+    xb = autort.ops.attention_f16(q, b_sk, b_sv, att_f)
+    ref = cport.attention_decode(q.cpu().numpy(), kc.cpu().numpy(), vc.cpu().numpy(), pos + 1, 1 / math.sqrt(head_size))
+    assert _err(xb.cpu().numpy(), ref) <= 1e-2
+    xb32 = autort.ops.attention_f32(q.float(), b_sk.float(), b_sv.float(), att_f)
+    assert _err(xb32.cpu().numpy(), ref) <= 2e-3
+
+
+def test_legacy_custom_op_binding(cuda):
+    """frameworks/pytorch/custom_op.py protocol: CustomOp(ir, input_orders, device).tune().emit(); op(*inputs)."""
+    dev = autort.device()
+    qw, sc = packing.synth_w4(512, 256, 9)
+    x = packing.synth_x(1, 512, 10)[0]
+    t = dict(input0=torch.from_numpy(x).to(dev), qweight=torch.from_numpy(qw).to(dev), scales=torch.from_numpy(sc).to(dev))
+    op = CustomOp(ir=W4A16_IR, input_orders=t, device=dev).tune(step=0).emit()
+    y = op(t["input0"], t["qweight"], t["scales"])
+    assert _err(y.cpu().numpy(), cport.w4a16_gemm(x, qw, sc)) <= 1e-2
+    sm = CustomOp(ir="temp0[N] >=! input0[N, C]; temp1[N] +=! (input0[N, C] - temp0[N]).call(`exp`); "
+                     "output0[N, C] = (input0[N, C] - temp0[N]).call(`exp`) / temp1[N]",
+                  input_orders={"input0": (None, torch.float32, [32, 1024])}, device=dev).emit()
+    xs = torch.randn(32, 1024, device=dev)
+    assert torch.allclose(sm(xs), torch.softmax(xs, -1), atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        CustomOp(ir="output0[N] = input0[N] + input1[N]", input_orders={"input0": xs[0], "input1": xs[1]}, device=dev).emit()
