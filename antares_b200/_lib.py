@@ -30,6 +30,7 @@ SIGNATURES = {
     "ab200_w4a16_gemv_residual": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ab200_w4a16_gemv_f32out": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ab200_w4a16_gemv_fused": [_vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
+    "ab200_w4a16_gemv_static": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ab200_residual_add": [_vp, _vp, _i, _vp],
     "ab200_kernel_status": [_vp],
     "ab200_set_option": [ctypes.c_char_p, _i],

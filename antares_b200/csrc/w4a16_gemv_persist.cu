@@ -469,3 +469,46 @@ int gemv_persist_dispatch(const void *x, const __half *norm_w, float eps, const 
 }
 
 }  // namespace ab200
+
+// ---- entry point that allocates nothing ------------------------------------------------------------
+// Scratch for ab200_w4a16_gemv_static: lives in the library image, so every GPU that loads the
+// library holds it until the process exits.  Layout as for any other scratch of this kernel:
+// [64 KiB tile counters][K-slice partial sums].
+namespace {
+constexpr size_t STATIC_SCRATCH_BYTES = ab200::PERSIST_COUNTER_BYTES + (size_t)2 * 1024 * 1024;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the
+// address is looked up once per device (with that device current) and cached here.
+static void *g_static_scratch_ptr[64] = {nullptr};
+}  // namespace
+
+extern "C" int ab200_w4a16_gemv_static(const void *x, const int32_t *qweight, const void *scales, void *out, int M, int K, int N,
+                                       int group, void *stream) {
+  using namespace ab200;
+  clear_error();
+  AB200_REQUIRE(x && qweight && scales && out, "w4a16_gemv_static: null pointer");
+  AB200_REQUIRE(M >= 1 && M <= 16, "w4a16_gemv_static: M=%d outside 1..16", M);
+  AB200_REQUIRE(K > 0 && K % 128 == 0, "w4a16_gemv_static: K=%d must be a positive multiple of 128", K);
+  AB200_REQUIRE(group > 0 && group % 32 == 0 && K % group == 0, "w4a16_gemv_static: group=%d must be a multiple of 32 dividing K=%d", group, K);
+  AB200_REQUIRE(N > 0 && N % 4 == 0, "w4a16_gemv_static: N=%d must be a positive multiple of 4", N);
+  AB200_REQUIRE(aligned16(x) && aligned16(qweight) && aligned16(scales) && aligned16(out), "w4a16_gemv_static: pointers must be 16-byte aligned");
+  if (!gemv_persist_fits(M, K, N))
+    return fail(AB200_EUNSUPPORTED, "w4a16_gemv_static: x of %d x %d does not fit the kernel's shared memory", M, K);
+  const size_t need = gemv_persist_scratch_bytes(M, K, N);
+  if (need > STATIC_SCRATCH_BYTES)
+    return fail(AB200_EINVAL, "w4a16_gemv_static: M=%d K=%d N=%d needs %zu bytes of scratch, the built-in scratch holds %zu", M, K, N, need,
+                (size_t)STATIC_SCRATCH_BYTES);
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "w4a16_gemv_static: device index %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {  // first call on this device: resolve the symbol's device address
+    void *ptr = nullptr;
+    AB200_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  void *scratch = g_static_scratch_ptr[dev];
+  // The array keeps whatever the last call left: the tile counters must start at zero.
+  const size_t counter_bytes = (size_t)((N + P_TILE - 1) / P_TILE) * sizeof(int);
+  AB200_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, (cudaStream_t)stream));
+  return gemv_persist_dispatch(x, nullptr, 0.f, qweight, scales, out, M, K, N, group, PRO_PLAIN, EPI_STORE, scratch, (cudaStream_t)stream);
+}

@@ -118,6 +118,26 @@ int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_
                            void *stream);
 size_t ab200_w4a16_gemv_workspace_bytes(int M, int K, int N);
 
+/* ab200_w4a16_gemv for callers that may not allocate device memory.  No counterpart in the
+ * reference.  Some hosts hand a plugin no way to allocate: an inference server that reserves the
+ * whole device for its own memory pool at start-up and forbids driver allocations afterwards
+ * (they would fail, or stall every stream while the driver synchronises), or a real-time loop
+ * that must never block in the driver.  This entry point computes the same fp16 contraction
+ * with the split-K kernel, whose partial sums and tile counters live in a fixed 2 MiB + 64 KiB
+ * array inside the library image (each GPU that loads the library holds it until the process
+ * exits).  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - Limits: fp16 only, K % 128 == 0, x must fit the kernel's shared memory, and the K-slice
+ *     partials (slices * M * N * 4 bytes, as ab200_w4a16_gemv_workspace_bytes reports) must fit
+ *     the 2 MiB; larger requests return AB200_EINVAL with the sizes in the message.  All four
+ *     Llama-2-7B projections fit at batch 1, the three with K = 4096 up to batch 4.
+ *   - The first call on each device looks up the array's device address (that device must be
+ *     current); make that first call before any stream capture.
+ *   - Every call uses the same array, which keeps what the last call left; the counters are
+ *     cleared on `stream` before the launch.  Two calls that overlap on the GPU (different
+ *     streams, or this and another process-wide user of the array) race: serialise them. */
+int ab200_w4a16_gemv_static(const void *x, const int32_t *qweight, const void *scales, void *out,
+                            int M, int K, int N, int group, void *stream);
+
 /* x_f32[i] += fp16_round(partial_f32[i]) — the residual update of lines 168,173 applied to an
  * all-reduced partial. */
 int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream);
