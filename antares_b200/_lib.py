@@ -34,6 +34,12 @@ SIGNATURES = {
     "ab200_residual_add": [_vp, _vp, _i, _vp],
     "ab200_kernel_status": [_vp],
     "ab200_set_option": [ctypes.c_char_p, _i],
+    "ab200_comm_alloc": [_i, _i, _vp, _vp],
+    "ab200_comm_open": [_vp, _vp],
+    "ab200_comm_close": [_vp],
+    "ab200_comm_free": [_vp],
+    "ab200_allreduce_residual": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "ab200_allreduce_residual_emulated": [_vp, _vp, _i, _vp, _i, _i, _vp, _vp],
     "ab200_w4a16_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],
     "ab200_rmsnorm_vsum": [_vp, _vp, _vp, _vp, _sz, _f, _f, _i, _vp],
@@ -48,7 +54,8 @@ SIGNATURES = {
     "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_greedy_next": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp],
 }
-OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version", "ab200_w4a16_gemv_workspace_bytes"]
+OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version", "ab200_w4a16_gemv_workspace_bytes", "ab200_comm_buffer_bytes",
+                 "ab200_comm_emulation_scratch_bytes"]
 
 _lib = None
 
@@ -70,6 +77,10 @@ def load():
         L.ab200_abi_version.restype = ctypes.c_int
         L.ab200_w4a16_gemv_workspace_bytes.restype = ctypes.c_size_t
         L.ab200_w4a16_gemv_workspace_bytes.argtypes = [_i, _i, _i]
+        L.ab200_comm_buffer_bytes.restype = ctypes.c_size_t
+        L.ab200_comm_buffer_bytes.argtypes = [_i, _i]
+        L.ab200_comm_emulation_scratch_bytes.restype = ctypes.c_size_t
+        L.ab200_comm_emulation_scratch_bytes.argtypes = []
         _lib = L
     return _lib
 

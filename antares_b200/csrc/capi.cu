@@ -21,6 +21,18 @@ int fail(int code, const char *fmt, ...) {
 
 void clear_error() { g_err[0] = 0; }
 
+int *kernel_error_ptr() {
+  static int *cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kernel_error) != cudaSuccess) return nullptr;
+    cached[dev] = reinterpret_cast<int *>(p);
+  }
+  return cached[dev];
+}
+
 static bool g_pdl = false;
 bool pdl_enabled() { return g_pdl; }
 void pdl_set(bool on) { g_pdl = on; }

@@ -34,11 +34,13 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
   } while (0)
 
 int sm_count();  // SMs of the current device (cached per device)
+int *kernel_error_ptr();  // device address of the status word that ab200_kernel_status reads (nullptr on failure)
 
 // Programmatic dependent launch: when enabled (option "pdl"), kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization, so a kernel's preamble (weight prefetch)
 // overlaps the tail of the kernel before it; every kernel executes griddepcontrol.wait before
 // touching data an earlier kernel produced.
+void comm_set_wait_polls(unsigned polls);
 bool pdl_enabled();
 void pdl_set(bool on);
 

@@ -413,6 +413,9 @@ int gemv_tuning_set(const char *name, int value) {
   if (!strcmp(name, "gemv_cluster")) {
     if (!(value == 0 || value == 1 || value == 2 || value == 4 || value == 8)) return fail(AB200_EINVAL, "gemv_cluster must be 0, 1, 2, 4 or 8");
     g_tune.cluster = value;
+  } else if (!strcmp(name, "comm_wait_polls")) {
+    if (value < 1) return fail(AB200_EINVAL, "comm_wait_polls must be positive");
+    comm_set_wait_polls((unsigned)value);
   } else if (!strcmp(name, "pdl")) {
     pdl_set(value != 0);
   } else if (!strcmp(name, "gemv_depth")) {

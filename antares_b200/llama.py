@@ -168,6 +168,10 @@ class LlamaInt4Decoder:
         """Row-parallel projection + residual: fused when alone, all-reduce of fp32 partials otherwise."""
         if self.world == 1:
             self._proj(x, q, s, self.x, prologue, 1)
+        elif hasattr(self.comm, "all_reduce_residual_"):
+            self._proj(x, q, s, self.partial, prologue, 2)
+            self.comm.all_reduce_residual_(self.x, self.partial)   # push all-reduce + residual in one kernel
+            self._n += 1
         else:
             self._proj(x, q, s, self.partial, prologue, 2)
             self.comm.all_reduce_sum_(self.partial)

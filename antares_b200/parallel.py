@@ -54,3 +54,55 @@ class TorchComm:
         t = torch.tensor([float(v)], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return float(t.item())
+
+
+class PushComm(TorchComm):
+    """TorchComm plus the one-shot push all-reduce over NVLink peer memory (csrc/comm.cu): every
+    rank owns a receive buffer, maps its peers' buffers through CUDA IPC and the exchange is one
+    kernel per rank (peer stores, epoch flags, bounded wait, rank-ordered sum fused with the
+    residual update).  torch.distributed is used only to swap the 64-byte IPC handles."""
+
+    def __init__(self, device, n_max, group=None):
+        import ctypes
+        from ._lib import call
+        super().__init__(group)
+        self.device, self.n_max = device, int(n_max)
+        torch.cuda.set_device(device)
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        call("ab200_comm_alloc", self.world, self.n_max, ctypes.cast(ctypes.pointer(ptr), ctypes.c_void_p), ctypes.cast(handle, ctypes.c_void_p))
+        self._own = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self._peers = []
+        bufs = (ctypes.c_void_p * self.world)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                bufs[r] = self._own
+            else:
+                p = ctypes.c_void_p()
+                hb = ctypes.create_string_buffer(h, 64)
+                call("ab200_comm_open", ctypes.cast(hb, ctypes.c_void_p), ctypes.cast(ctypes.pointer(p), ctypes.c_void_p))
+                bufs[r] = p.value
+                self._peers.append(p.value)
+        self._bufs = bufs
+        dist.barrier(group=group)
+
+    def all_reduce_residual_(self, x_f32, partial_f32):
+        """x += fp16_round(sum over ranks of partial): one kernel, no NCCL."""
+        import ctypes
+        from ._lib import call
+        call("ab200_allreduce_residual", x_f32.data_ptr(), partial_f32.data_ptr(), x_f32.numel(),
+             ctypes.cast(self._bufs, ctypes.c_void_p), self.rank, self.world, self.n_max, torch.cuda.current_stream().cuda_stream)
+        return x_f32
+
+    def close(self):
+        from ._lib import call
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self._peers:
+            call("ab200_comm_close", p)
+        self._peers = []
+        if self._own:
+            call("ab200_comm_free", self._own)
+            self._own = None

@@ -259,12 +259,15 @@ def run_ours(args):
     import torch
     from antares_b200 import parallel
     from antares_b200.llama import LlamaConfig, LlamaInt4Decoder, synth_prompt
+    os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout: one JSON line only
     rank, world, local_rank = parallel.init_from_env()
     if world != args.gpus:
         raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d (launch N>1 with torch.distributed.run)" % (args.gpus, world))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    comm = parallel.TorchComm() if world > 1 else None
+    comm = None
+    if world > 1:
+        comm = parallel.TorchComm() if args.comm == "nccl" else parallel.PushComm(dev, 4096)
     K, W = args.steps, max(3, args.warmup)
     cfg = LlamaConfig(max_seq=N_PROMPT + W + K + 8)
     dec = LlamaInt4Decoder(cfg, dev, rank=rank, world=world, comm=comm, max_tokens=N_PROMPT + W + K + 8)
@@ -323,7 +326,7 @@ def run_ours(args):
             "ms_per_step": 1e3 * sec / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "llama2-7b-arch int4 g128 greedy decode, batch 1, %d prompt tokens then %d timed tokens" % (N_PROMPT, K),
-                       "parallelism": "tp%d" % world, "l2": "each step streams %.2f GB of weights per GPU (> L2), no flush needed" % (step_bytes / 1e9),
+                       "parallelism": "tp%d" % world, "allreduce": ("none" if world == 1 else args.comm), "l2": "each step streams %.2f GB of weights per GPU (> L2), no flush needed" % (step_bytes / 1e9),
                        "launcher": "cuda graph, 1 replay per token"},
             "e2e": {"value": K / sec_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": dec.launches_per_step * K, "launches_per_step": dec.launches_per_step,
@@ -344,6 +347,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--comm", default="push", choices=["push", "nccl"], help="all-reduce of row-parallel partials: one-shot NVLink push kernel or NCCL")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:

@@ -50,6 +50,7 @@ int ab200_kernel_status(int *status_host);
  * (samples/05_llama2_7b_int4.py:139).  Names: "gemv_cluster" (0 = auto, 1/2/4/8 K-slices per
  * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA),
  * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel).
+ * "comm_wait_polls": polls after which the push all-reduce gives up waiting for a peer.
  * "pdl" (0/1): launch kernels with programmatic dependent launch so that a kernel's weight
  * prefetch overlaps the tail of its predecessor in the stream.  Process-wide; host call. */
 int ab200_set_option(const char *name, int value);
@@ -213,6 +214,42 @@ int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, in
  * For tensor-parallel vocab shards use vocab_offset and a later ab200_argmax_merge. */
 int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
                       int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
+
+/* ---- tensor-parallel exchange over NVLink peer memory -----------------------------------------
+ * The reference's only collectives are NCCL calls inside its TensorFlow plugin
+ * (frameworks/tensorflow/communicate_ops.cc:65-99 bootstrap, :191 ncclAllReduce); its Llama
+ * samples are single-device.  These entry points give the tensor-parallel decode step a one-shot
+ * push all-reduce: one process per GPU, each rank owns a receive buffer, peers map it through
+ * CUDA IPC and store into it directly.  No multicast objects are used. */
+
+/* Bytes of one rank's receive buffer for `world` ranks and messages of up to n_max floats. */
+size_t ab200_comm_buffer_bytes(int world, int n_max);
+/* Allocates (cudaMalloc) and zeroes this rank's receive buffer on the current device and, if
+ * ipc_handle64_host is not NULL, writes its 64-byte CUDA IPC handle there.  Set-up call:
+ * allocates and synchronises. */
+int ab200_comm_alloc(int world, int n_max, void **buf_out, void *ipc_handle64_host);
+/* Maps a peer's receive buffer from its IPC handle (peer access is enabled on demand). */
+int ab200_comm_open(const void *ipc_handle64_host, void **peer_buf_out);
+int ab200_comm_close(void *peer_buf);
+int ab200_comm_free(void *buf);
+
+/* x_f32[0..n) += fp16_round(sum over ranks of partial_f32[0..n)) in one kernel per rank:
+ * peer stores of the partial into every rank's buffer, epoch flags, a bounded wait for all
+ * ranks, summation in rank order (bit-identical on all ranks).  bufs_host[r] = rank r's buffer as
+ * mapped in this process (own entry = the local allocation).  Replaces
+ * `all_reduce(partial); x = x + partial` after the row-parallel projections.  A wait that runs out
+ * (a peer never arrived) is reported by ab200_kernel_status as site 100 + peer. */
+int ab200_allreduce_residual(float *x_f32, const float *partial_f32, int n, void *const *bufs_host,
+                             int rank, int world, int n_max, void *stream);
+
+/* The same protocol with all `world` ranks run as the blocks of ONE cooperative launch on one
+ * GPU (x_host[r], partial_host[r], bufs_host[r] = rank r's device pointers): lets the exchange
+ * be tested on fewer GPUs than ranks.  emu_scratch_dev: ab200_comm_emulation_scratch_bytes()
+ * bytes of device memory.  Synchronises the stream once while setting up. */
+int ab200_allreduce_residual_emulated(float *const *x_host, const float *const *partial_host, int n,
+                                      void *const *bufs_host, int world, int n_max,
+                                      void *emu_scratch_dev, void *stream);
+size_t ab200_comm_emulation_scratch_bytes(void);
 
 #ifdef __cplusplus
 }
