@@ -1,11 +1,265 @@
-// W4A16 prefill GEMM on the 5th-generation tensor cores (placeholder until the tcgen05 kernel lands).
+// W4A16 prefill GEMM on the 5th-generation tensor cores: out[M,N] = x[M,K] . dequant(qweight, scales)
+// with fp16 x / scales / out and fp32 accumulation in tensor memory.
+//
+// Replaces the exported op of samples/05_llama2_7b_int4.py:135-144 when it is called with a leading
+// M axis larger than the decode path handles.  The dequantised weight fed to the tensor cores is
+// exactly w = RN_fp16(scale * fp16(q - 8)) (IR statement 2), the products accumulate in fp32.
+//
+// CTA tile 128 (M) x 256 (N), K step 64, two shared-memory stages.  All 256 threads fill a stage:
+//   A: x tile, 16-byte chunks copied into the K-major "core matrix" layout (8 rows x 16 B
+//      contiguous), each chunk's 8 k-values permuted to (k0,k4,k1,k5,k2,k6,k3,k7);
+//   B: thread t owns column n0 + t: each packed int32 word (8 consecutive k of one column) becomes
+//      one 16-byte row of a core matrix in the same k order (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the
+//      zero-point, HMUL2 by the group scale), so no transpose is needed and a quarter-warp writes
+//      128 contiguous bytes.
+// Since both operands carry the same permutation of k inside every group of 8, the contraction
+// is unchanged.  One thread then issues four `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
+// both operands K-major, no swizzle) per stage and commits them to an mbarrier; filling stage
+// s+1 overlaps the MMAs of stage s.  The 128x256 fp32 accumulator lives in 256 TMEM columns;
+// the epilogue reads it with `tcgen05.ld` (row = TMEM lane = thread), rounds to fp16 and stores.
+// Every mbarrier wait is bounded and reports through the status word.
 #include "common.cuh"
+
+namespace ab200 {
+
+constexpr int GM_BM = 128, GM_BN = 256, GM_BK = 64;
+constexpr int GM_THREADS = 256;
+constexpr int GM_STAGES = 2;
+constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;  // 16 KiB
+constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;  // 32 KiB
+constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
+constexpr unsigned GM_WAIT_POLLS = 1u << 22;
+
+struct GemmParams {
+  const __half *x;
+  const int32_t *qw;
+  const __half *scales;
+  __half *out;
+  int M, K, N, group;
+  int *status;
+};
+
+__device__ __forceinline__ uint32_t gm_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes;
+// LBO = bytes between the two 16-byte K chunks of one MMA, SBO = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t gm_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  return d;                // base offset 0, layout type 0 (no swizzle)
+}
+
+__device__ __forceinline__ bool gm_mbar_wait(uint64_t *bar, unsigned parity) {
+  const uint32_t addr = gm_smem_u32(bar);
+  for (unsigned i = 0; i < GM_WAIT_POLLS; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char gm_smem[];
+  __shared__ __align__(8) uint64_t mma_bar[GM_STAGES];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int fail_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * GM_BN;
+  const int K = p.K, N = p.N, M = p.M;
+
+  if (tid == 0) {
+    for (int s = 0; s < GM_STAGES; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&mma_bar[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fail_s = 0;
+  }
+  if (warp == 0) {  // one warp allocates the accumulator's 256 TMEM columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(&tmem_base_s)), "r"(GM_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = tmem_base_s;
+
+  // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+
+  // ---- per-thread fill roles ---------------------------------------------------------------------------
+  // B: column n0 + tid (clamped), eight packed rows per stage
+  int nb = n0 + tid;
+  const bool nb_ok = nb < N;
+  if (!nb_ok) nb = N - 1;
+  const int32_t *bq = p.qw + nb;                      // + row * N
+  const __half *bs = p.scales + nb;                   // + (k / group) * N
+  const uint32_t b_off = (uint32_t)((tid >> 3) * 128 + (tid & 7) * 16);  // core matrix row of this column; + kc * 4096
+  // A: four 16-byte chunks per stage: row group mg, k chunk kc, row r8
+  const int r8 = lane & 7, kq = lane >> 3;
+  const __half *ax[4];
+  uint32_t a_off[4];
+  bool a_ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int mg = warp * 2 + (i >> 1), kc = (i & 1) * 4 + kq;
+    const int row = m0 + mg * 8 + r8;
+    a_ok[i] = row < M;
+    ax[i] = p.x + (size_t)(a_ok[i] ? row : 0) * K + kc * 8;
+    a_off[i] = (uint32_t)((kc * 16 + mg) * 128 + r8 * 16);
+  }
+
+  uint32_t breg[8];
+  uint4 areg[4];
+  __half sreg;
+  auto load_regs = [&](int kt) {  // global -> registers for k tile kt
+    const int row0 = kt * (GM_BK / 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) breg[j] = (uint32_t)__ldg(bq + (size_t)(row0 + j) * N);
+    sreg = __ldg(bs + (size_t)((kt * GM_BK) / p.group) * N);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) areg[i] = a_ok[i] ? __ldg(reinterpret_cast<const uint4 *>(ax[i] + (size_t)kt * GM_BK)) : make_uint4(0, 0, 0, 0);
+  };
+
+  const int ktiles = K / GM_BK;
+  load_regs(0);
+  bool ok = true;
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int s = kt % GM_STAGES;
+    unsigned char *sa = gm_smem + s * GM_STAGE_BYTES, *sb = sa + GM_A_BYTES;
+    if (kt >= GM_STAGES) {  // the MMAs that read this stage two iterations ago must have finished
+      if (!gm_mbar_wait(&mma_bar[s], ((kt / GM_STAGES) - 1) & 1)) {
+        ok = false;
+        fail_s = 1;
+      }
+    }
+    // ---- fill the stage from registers -------------------------------------------------------------
+    {
+      constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
+      const __half2 c1032 = u2h2(0x64086408u), c16th = u2h2(0x2C002C00u), cm72 = u2h2(0xD480D480u);
+      const __half2 sc2 = __half2half2(sreg);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w = breg[j], w8 = w >> 8;
+        uint4 o;  // (k0,k4)(k1,k5)(k2,k6)(k3,k7), each RN_fp16(scale * (q - 8))
+        o.x = h22u(__hmul2(__hsub2(u2h2(lop3<0xEA>(w, LO, MAGIC)), c1032), sc2));
+        o.y = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w, HI, MAGIC)), c16th, cm72), sc2));
+        o.z = h22u(__hmul2(__hsub2(u2h2(lop3<0xEA>(w8, LO, MAGIC)), c1032), sc2));
+        o.w = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w8, HI, MAGIC)), c16th, cm72), sc2));
+        if (!nb_ok) o = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(sb + j * (GM_BN / 8) * 128 + b_off) = o;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = areg[i];
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        *reinterpret_cast<uint4 *>(sa + a_off[i]) = o;
+      }
+    }
+    if (kt + 1 < ktiles) load_regs(kt + 1);  // next tile's global loads fly during the MMAs
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_base = gm_smem_u32(sa), b_base = gm_smem_u32(sb);
+#pragma unroll
+      for (int kb = 0; kb < GM_BK / 16; ++kb) {
+        const uint64_t da = gm_desc(a_base + kb * 2 * (GM_BM / 8) * 128, (GM_BM / 8) * 128, 128);
+        const uint64_t db = gm_desc(b_base + kb * 2 * (GM_BN / 8) * 128, (GM_BN / 8) * 128, 128);
+        const uint32_t accumulate = (kt > 0 || kb > 0) ? 1u : 0u;
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc),
+            "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
+            : "memory");
+      }
+      // arrives on the barrier when every MMA issued so far has completed
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
+    }
+  }
+  // ---- drain: the last commit covers every MMA -----------------------------------------------------
+  {
+    const int last = ktiles - 1, s = last % GM_STAGES;
+    if (!gm_mbar_wait(&mma_bar[s], (last / GM_STAGES) & 1)) {
+      ok = false;
+      fail_s = 1;
+    }
+  }
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (fail_s && tid == 0) atomicExch(p.status, 200);
+
+  // ---- epilogue: TMEM -> registers -> fp16 -> global; warps 0-3, thread = accumulator row ------------
+  if (warp < 4 && !fail_s) {
+    const int row = m0 + warp * 32 + lane;
+    const uint32_t taddr = tmem_acc + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < GM_BN; c += 16) {
+      uint32_t r[16];
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+            "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          : "r"(taddr + c));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < M) {
+        __half *o = p.out + (size_t)row * N + n0 + c;
+        if (n0 + c + 16 <= N) {
+          uint4 h0, h1;
+          h0.x = h22u(__floats2half2_rn(__uint_as_float(r[0]), __uint_as_float(r[1])));
+          h0.y = h22u(__floats2half2_rn(__uint_as_float(r[2]), __uint_as_float(r[3])));
+          h0.z = h22u(__floats2half2_rn(__uint_as_float(r[4]), __uint_as_float(r[5])));
+          h0.w = h22u(__floats2half2_rn(__uint_as_float(r[6]), __uint_as_float(r[7])));
+          h1.x = h22u(__floats2half2_rn(__uint_as_float(r[8]), __uint_as_float(r[9])));
+          h1.y = h22u(__floats2half2_rn(__uint_as_float(r[10]), __uint_as_float(r[11])));
+          h1.z = h22u(__floats2half2_rn(__uint_as_float(r[12]), __uint_as_float(r[13])));
+          h1.w = h22u(__floats2half2_rn(__uint_as_float(r[14]), __uint_as_float(r[15])));
+          *reinterpret_cast<uint4 *>(o) = h0;
+          *reinterpret_cast<uint4 *>(o + 8) = h1;
+        } else {
+          for (int j = 0; j < 16; ++j)
+            if (n0 + c + j < N) o[j] = __float2half_rn(__uint_as_float(r[j]));
+        }
+      }
+    }
+  }
+  (void)ok;
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(GM_BN) : "memory");
+}
+
+}  // namespace ab200
 
 using namespace ab200;
 
-extern "C" int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const void *scales, void *out, int M, int K,
-                                int N, int group, int dtype, void *stream) {
+extern "C" int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const void *scales, void *out, int M, int K, int N,
+                                int group, int dtype, void *stream) {
   clear_error();
-  (void)x; (void)qweight; (void)scales; (void)out; (void)M; (void)K; (void)N; (void)group; (void)dtype; (void)stream;
-  return fail(AB200_EUNSUPPORTED, "w4a16_gemm: prefill kernel not built into this library");
+  AB200_REQUIRE(x && qweight && scales && out, "w4a16_gemm: null pointer");
+  if (dtype != AB200_F16) return fail(AB200_EUNSUPPORTED, "w4a16_gemm: the tensor-core path is built for float16 (dtype %d given)", dtype);
+  AB200_REQUIRE(M > 0 && N > 0 && N % 8 == 0, "w4a16_gemm: M=%d must be positive, N=%d a positive multiple of 8", M, N);
+  AB200_REQUIRE(K > 0 && K % GM_BK == 0, "w4a16_gemm: K=%d must be a positive multiple of %d", K, GM_BK);
+  AB200_REQUIRE(group >= GM_BK && group % GM_BK == 0 && K % group == 0, "w4a16_gemm: group=%d must be a multiple of %d dividing K", group, GM_BK);
+  AB200_REQUIRE(aligned16(x) && aligned16(qweight) && aligned16(scales) && aligned16(out), "w4a16_gemm: pointers must be 16-byte aligned");
+  int *status = kernel_error_ptr();
+  AB200_REQUIRE(status != nullptr, "w4a16_gemm: cannot resolve the status word");
+  GemmParams p{(const __half *)x, qweight, (const __half *)scales, (__half *)out, M, K, N, group, status};
+  const size_t smem = (size_t)GM_STAGES * GM_STAGE_BYTES + 1024;
+  AB200_CUDA(cudaFuncSetAttribute(w4a16_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const dim3 grid((N + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM);
+  w4a16_gemm_tcgen05_kernel<<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(p);
+  AB200_CHECK_LAUNCH("w4a16_gemm");
+  return AB200_OK;
 }

@@ -38,9 +38,9 @@ N_PROMPT = 128
 METRIC = "llama2_7b_int4_decode_tokens_per_s"
 UNIT = "tokens/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate|up GEMV launch (4096 -> 22016), from
-# the ncu capture summarised in profiles/; None until measured.
-NCU_TRAFFIC_GATE_UP = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate|up GEMV launch (K=4096, N=22016, M=1) from the
+# ncu capture summarised in profiles/w4a16_gemv_scalar_gate_up_m1.md (algorithmic bytes: 46,550,016).
+NCU_TRAFFIC_GATE_UP = 46533888 + 2560
 
 
 def measured_peaks():

@@ -182,3 +182,37 @@ def test_fused_rmsnorm_prologue_and_residual_epilogue(cuda, M):
     resid = _dev(resid0, cuda)
     ops.w4a16_gemv_fused(_dev(gu, cuda), _dev(qw2, cuda), _dev(sc2, cuda), resid, prologue=ops.PRO_SILU_MUL, epilogue=ops.EPI_RESIDUAL)
     assert _err(resid.cpu().numpy(), ref2) <= TOL
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 128, 256), (256, 512, 512), (130, 256, 264), (17, 4096, 1000), (384, 11008, 512)])
+def test_prefill_gemm_tcgen05_matches_oracle(cuda, M, K, N):
+    """W4A16 GEMM on tcgen05/TMEM: same arithmetic as the decode path, M beyond 16, ragged tiles."""
+    qw, sc = packing.synth_w4(K, N, 51)
+    x = packing.synth_x(M, K, 52)
+    ref = cport.w4a16_gemm(x, qw, sc)
+    y = ops.w4a16_gemm(_dev(x, cuda), _dev(qw, cuda), _dev(sc, cuda))
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert _err(y.cpu().numpy(), ref) <= TOL
+    assert ops.w4a16_matmul(_dev(x, cuda), _dev(qw, cuda), _dev(sc, cuda)).shape == (M, N)
+
+
+def test_prefill_gemm_config3_full_size(cuda):
+    """BASELINE config 3: x fp16 [2048, 4096], W 4096 -> 11008, g=128.  All rows computed on the GPU; a
+    seeded sample of 64 rows is checked against the oracle, the rest through linearity."""
+    M, K, N = 2048, 4096, 11008
+    qw, sc = packing.synth_w4(K, N, 61)
+    x = packing.synth_x(M, K, 62)
+    qd, sd, xd = _dev(qw, cuda), _dev(sc, cuda), _dev(x, cuda)
+    y = ops.w4a16_gemm(xd, qd, sd)
+    rows = np.random.default_rng(63).choice(M, 64, replace=False)
+    ref = cport.w4a16_gemm(np.ascontiguousarray(x[rows]), qw, sc)
+    assert _err(y[torch.from_numpy(rows).to(cuda)].cpu().numpy(), ref) <= TOL
+    # the decode kernel and the tensor-core kernel agree on the same rows
+    y16 = ops.w4a16_gemv(xd[:16].contiguous(), qd, sd)
+    assert (y[:16].float() - y16.float()).abs().max() <= TOL * y16.float().abs().max()
+    # linearity over the whole batch: f(x_a + x_b) = f(x_a) + f(x_b)
+    y2 = ops.w4a16_gemm((xd[:1024] * 0.5 + xd[1024:]).contiguous(), qd, sd)
+    lin = y[:1024].float() * 0.5 + y[1024:].float()
+    assert (y2.float() - lin).abs().max() <= TOL * lin.abs().max()
+    assert ops.kernel_status() == 0
