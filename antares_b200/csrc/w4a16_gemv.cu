@@ -63,31 +63,39 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   float *red = reinterpret_cast<float *>(smem_raw + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));
   float *part = red + GEMV_WARPS * M * TILE_N;
 
-  const int32_t *qcol = p.qw + n0;
-  const __half *scol = reinterpret_cast<const __half *>(p.scales) + n0;
+  // Streaming state: bumped pointers only (no multiplies or divisions per unit, no column
+  // predicate: out-of-range columns are clamped to the last valid chunk and dropped at the store).
+  const int n0c = col_ok ? n0 : p.N - 4;
+  int u = u_begin + warp;
+  const unsigned row_step = (unsigned)p.N / 4;                      // uint4 elements between packed rows
+  const uint4 *wp = reinterpret_cast<const uint4 *>(p.qw + (size_t)u * UNIT_ROWS * p.N + n0c);
+  const unsigned unit_step = row_step * UNIT_ROWS * GEMV_WARPS;     // to this warp's next unit
+  // scales: the warp advances 8 units = 256 k per round; for the usual group sizes that is a whole
+  // number of scale rows, otherwise the row is recomputed per unit
+  const bool s_fast = (UNIT_K * GEMV_WARPS) % p.group == 0;
+  const unsigned s_step = (unsigned)((UNIT_K * GEMV_WARPS) / p.group) * p.N;
+  const __half *scol = reinterpret_cast<const __half *>(p.scales) + n0c;
+  const __half *sp = scol + (size_t)((u * UNIT_K) / p.group) * p.N;
 
   constexpr int NBUF = 2;  // units in flight per warp (registers)
   uint4 wbuf[NBUF][UNIT_ROWS];
   uint2 sbuf[NBUF];
-  auto load_unit = [&](int u, int b) {
-    if (col_ok) {
-      const int32_t *q = qcol + (size_t)u * UNIT_ROWS * p.N;
+  int u_load = u;  // unit that the next load_unit() fetches
+  auto load_unit = [&](int b) {
 #pragma unroll
-      for (int r = 0; r < UNIT_ROWS; ++r) wbuf[b][r] = ldg_stream_v4(q + (size_t)r * p.N);
-      sbuf[b] = ldg_nc_v2(scol + (size_t)((u * UNIT_K) / p.group) * p.N);
-    } else {
-#pragma unroll
-      for (int r = 0; r < UNIT_ROWS; ++r) wbuf[b][r] = make_uint4(0, 0, 0, 0);
-      sbuf[b] = make_uint2(0, 0);
-    }
+    for (int r = 0; r < UNIT_ROWS; ++r) wbuf[b][r] = ldg_stream_v4(wp + r * row_step);
+    sbuf[b] = ldg_nc_v2(sp);
+    wp += unit_step;
+    u_load += GEMV_WARPS;
+    if (s_fast) sp += s_step;
+    else sp = scol + (size_t)((u_load * UNIT_K) / p.group) * p.N;
   };
 
   pdl_launch_dependents();
-  int u = u_begin + warp;
   // the first NBUF units of this warp are on their way before x is staged
 #pragma unroll
   for (int b = 0; b < NBUF; ++b)
-    if (u + b * GEMV_WARPS < u_end) load_unit(u + b * GEMV_WARPS, b);
+    if (u_load < u_end) load_unit(b);
   pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
@@ -164,18 +172,19 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 #pragma unroll
     for (int c = 0; c < 4; ++c) facc[m][c] = 0.f;
 
-  auto compute_unit = [&](int uu, int b) {
+  const uint4 *xp = reinterpret_cast<const uint4 *>(xs) + warp * UNIT_ROWS;  // this warp's unit within the slice
+  const unsigned xm_step = (unsigned)xs_stride / 8;                            // uint4 elements between batch rows
+  auto compute_unit = [&](int b) {
     __half2 hacc[M][4];
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) hacc[m][c] = __half2half2(__ushort_as_half(0));
-    const __half *xu = xs + (uu - u_begin) * UNIT_K;
+      for (int c = 0; c < 4; ++c) hacc[m][c] = u2h2(0u);
 #pragma unroll
     for (int r = 0; r < UNIT_ROWS; ++r) {
       uint4 xr[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) xr[m] = *reinterpret_cast<const uint4 *>(xu + (size_t)m * xs_stride + r * 8);
+      for (int m = 0; m < M; ++m) xr[m] = xp[m * xm_step + r];
       const uint32_t wr[4] = {wbuf[b][r].x, wbuf[b][r].y, wbuf[b][r].z, wbuf[b][r].w};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -199,6 +208,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
         const float2 f = __half22float2(hacc[m][c]);
         facc[m][c] = fmaf(sc[c], f.x + f.y, facc[m][c]);
       }
+    xp += UNIT_ROWS * GEMV_WARPS;
   };
 
   // NBUF-deep software pipeline over this warp's units: a buffer is refilled as soon as it is consumed.
@@ -206,8 +216,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 #pragma unroll
     for (int b = 0; b < NBUF; ++b) {
       if (u < u_end) {
-        compute_unit(u, b);
-        if (u + NBUF * GEMV_WARPS < u_end) load_unit(u + NBUF * GEMV_WARPS, b);
+        compute_unit(b);
+        if (u_load < u_end) load_unit(b);
       }
       u += GEMV_WARPS;
     }

@@ -255,6 +255,67 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
             "launches": n_launch, "avg_launch_us": sec / n_launch * 1e6, "algorithmic_bytes_per_step": alg}
 
 
+def extras_single_ops(torch, dev, peak_gbs, tensor_peak):
+    """Operator-level figures next to the headline (rank 0, N=1): the W4A16 prefill GEMM of BASELINE
+    config 3 on the tensor cores and the four decode GEMV shapes of config 2 at batch 1, each timed
+    alone with CUDA events (GEMVs rotate through weight copies larger than L2)."""
+    import numpy as np
+    from antares_b200 import ops, packing
+    out = {}
+    M, K, N = 2048, 4096, 11008
+    qw, sc = packing.synth_w4(K, N, 1)
+    qd, sd = torch.from_numpy(qw).to(dev), torch.from_numpy(sc).to(dev)
+    x = torch.from_numpy(packing.synth_x(M, K, 2)).to(dev)
+    y = torch.empty((M, N), dtype=torch.float16, device=dev)
+    for _ in range(3):
+        ops.w4a16_gemm(x, qd, sd, y)
+    ts = []
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.w4a16_gemm(x, qd, sd, y)
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ms = float(np.median(ts))
+    tf = 2.0 * M * K * N / ms / 1e9
+    out["prefill_gemm"] = {"shape": [M, K, N], "ms": ms, "tflops": tf, "peak_tflops": tensor_peak, "frac": tf / tensor_peak,
+                           "kernel": "w4a16_gemm_tcgen05_kernel"}
+    del qd, sd, x, y
+    gemv = {}
+    for name, (K, N) in (("o", (4096, 4096)), ("vqk", (4096, 12288)), ("gate_up", (4096, 22016)), ("down", (11008, 4096))):
+        qw, sc = packing.synth_w4(K, N, 3)
+        nbuf = int(300e6 // (qw.nbytes + sc.nbytes)) + 2
+        qs = [torch.from_numpy(qw).to(dev) for _ in range(nbuf)]
+        ss = [torch.from_numpy(sc).to(dev) for _ in range(nbuf)]
+        x = torch.from_numpy(packing.synth_x(1, K, 4)).to(dev)
+        y = torch.empty((1, N), dtype=torch.float16, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(3):
+                ops.w4a16_gemv(x, qs[i % nbuf], ss[i % nbuf], y)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(2 * nbuf):
+                    ops.w4a16_gemv(x, qs[i % nbuf], ss[i % nbuf], y)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (2 * nbuf)
+        torch.cuda.current_stream().wait_stream(side)
+        alg = K * N // 2 + (K // 128) * N * 2 + K * 2 + N * 2
+        gemv[name] = {"K": K, "N": N, "us": us, "GBs": alg / us / 1e3, "frac": alg / us / 1e3 / peak_gbs}
+        del qs, ss, g
+    out["gemv_m1"] = gemv
+    return out
+
+
 def run_ours(args):
     import torch
     from antares_b200 import parallel
@@ -335,6 +396,15 @@ def run_ours(args):
                          "frac_of_peak": step_bytes / (sec / K) / 1e9 / peak},
             "tokens_match_between_runs": bool((tokens == tokens_e2e).all()),
             "first_generated": [int(t) for t in tokens[N_PROMPT:N_PROMPT + 8]]}
+    if world == 1 and not args.no_extras:
+        tensor_peak = 1642.0
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                tensor_peak = float(json.load(f).get("bf16_tflops", tensor_peak))
+        del dec
+        torch.cuda.empty_cache()
+        line["extras"] = extras_single_ops(torch, dev, peak, tensor_peak)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = run_reference(argparse.Namespace(steps=20, warmup=0, gpus=1), as_baseline=True)
     return line
@@ -347,6 +417,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the operator-level figures (prefill GEMM, GEMV set)")
     ap.add_argument("--comm", default="push", choices=["push", "nccl"], help="all-reduce of row-parallel partials: one-shot NVLink push kernel or NCCL")
     args = ap.parse_args()
     if args.impl == "reference":
