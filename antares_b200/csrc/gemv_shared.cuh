@@ -77,6 +77,23 @@ __device__ __forceinline__ void unpack_pair(uint32_t w0, uint32_t w1, uint32_t (
   hi[3] = h22u(__hfma2(u2h2(lop3<0xEA>(w1s, HI, MAGIC)), c16th, cm72));
 }
 
+// The same operand quads as raw fp16 bit patterns: a nibble q left in mantissa bits 0-3 is the
+// subnormal q * 2^-24, in bits 4-7 it is 16q * 2^-24.  No FP16-pipe instruction at all; the
+// caller divides the matching x values by 16 for the high nibbles, removes the zero-point
+// through -8 * sum(x), and rescales the fp32 sums by 2^24.
+__device__ __forceinline__ void unpack_pair_raw(uint32_t w0, uint32_t w1, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
+  const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+  lo[0] = w0 & LO;
+  lo[1] = w1 & LO;
+  lo[2] = w0 & HI;
+  lo[3] = w1 & HI;
+  hi[0] = w0s & LO;
+  hi[1] = w1s & LO;
+  hi[2] = w0s & HI;
+  hi[3] = w1s & HI;
+}
+
 // Cross-warp, then cross-CTA (cluster) reduction of per-thread fp32 partials, and the epilogue.
 // Warps 0..NWARPS-1 hold partials (facc[m][c] for columns lane*4+c); every thread of the CTA
 // must call this (it contains CTA and cluster barriers).  The order of every sum is fixed, so

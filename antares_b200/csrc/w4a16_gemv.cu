@@ -40,7 +40,23 @@ struct GemvParams {
   int xs_stride;  // elements between batch rows of x in shared memory (same in every CTA of a cluster)
   const __half *norm_w = nullptr;  // PRO_RMSNORM: fp16 [K]
   float eps = 0.f;
+  // L2 prefetch hint: up to two byte ranges (the next projection's packed weights and scales)
+  const unsigned char *pf[2] = {nullptr, nullptr};
+  unsigned pf_bytes[2] = {0, 0};
 };
+
+constexpr unsigned PF_CHUNK = 16 * 1024;
+// One thread per CTA asks the TMA unit to pull this CTA's share of the hinted ranges into L2.
+__device__ __forceinline__ void issue_prefetch_hint(const GemvParams &p) {
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const unsigned bytes = p.pf_bytes[r];
+    for (unsigned off = blockIdx.x * PF_CHUNK; off < bytes; off += gridDim.x * PF_CHUNK) {
+      const unsigned n = (bytes - off < PF_CHUNK) ? ((bytes - off) & ~15u) : PF_CHUNK;
+      if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf[r] + off), "r"(n) : "memory");
+    }
+  }
+}
 
 // PRO selects how x is built in shared memory: plain fp16 x; RMSNorm of an fp32 row (every CTA
 // recomputes the row's sum of squares from L2: 16 KiB for K = 4096); SiLU(gate) * up of an fp16
@@ -96,6 +112,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 #pragma unroll
   for (int b = 0; b < NBUF; ++b)
     if (u_load < u_end) load_unit(b);
+  if (threadIdx.x == GEMV_THREADS - 1) issue_prefetch_hint(p);
   pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
@@ -403,7 +420,22 @@ static int gemv_f16_scalar(GemvParams p, int M, int epi, cudaStream_t s) {
 // (lowest fixed cost and best streaming rate at that size), 3-16 rows on the cluster warp-MMA
 // kernel (constant cost in the batch size).  The persistent warp-MMA kernel (option gemv_impl=3)
 // needs scratch; scratch == nullptr means the library-owned buffer.
+// One-shot prefetch hint of the calling thread (ab200_w4a16_gemv_prefetch_hint): consumed by the
+// next fp16 GEMV call, whichever kernel it picks (only the scalar-pipe kernel acts on it).
+static thread_local const unsigned char *t_hint_ptr[2] = {nullptr, nullptr};
+static thread_local unsigned t_hint_bytes[2] = {0, 0};
+
+static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                         int K, int N, int group, int epi, void *scratch, cudaStream_t s);
 static int gemv_f16(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                    int K, int N, int group, int epi, void *scratch, cudaStream_t s) {
+  const int rc = gemv_f16_impl(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, scratch, s);
+  t_hint_ptr[0] = t_hint_ptr[1] = nullptr;
+  t_hint_bytes[0] = t_hint_bytes[1] = 0;
+  return rc;
+}
+
+static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
                     int K, int N, int group, int epi, void *scratch, cudaStream_t s) {
   const int impl = gemv_tuning_impl();
   const bool persist_ok = gemv_persist_fits(M, K, N) && N % 4 == 0;
@@ -418,10 +450,28 @@ static int gemv_f16(const void *x, int pro, const __half *norm_w, float eps, con
   GemvParams p{x, qw, scales, out, K, N, group, K / UNIT_K, 0};
   p.norm_w = norm_w;
   p.eps = eps;
+  for (int r = 0; r < 2; ++r) {
+    p.pf[r] = t_hint_ptr[r];
+    p.pf_bytes[r] = t_hint_bytes[r];
+  }
   if (pro == PRO_PLAIN) return gemv_f16_scalar<PRO_PLAIN>(p, M, epi, s);
   if (pro == PRO_RMSNORM) return gemv_f16_scalar<PRO_RMSNORM>(p, M, epi, s);
   return gemv_f16_scalar<PRO_SILU_MUL>(p, M, epi, s);
 }
+
+}  // namespace ab200
+extern "C" int ab200_w4a16_gemv_prefetch_hint(const void *p0, size_t bytes0, const void *p1, size_t bytes1) {
+  using namespace ab200;
+  clear_error();
+  AB200_REQUIRE((!p0 || aligned16(p0)) && (!p1 || aligned16(p1)), "gemv_prefetch_hint: pointers must be 16-byte aligned");
+  AB200_REQUIRE(bytes0 < (1ull << 32) && bytes1 < (1ull << 32), "gemv_prefetch_hint: ranges are limited to 4 GiB");
+  t_hint_ptr[0] = reinterpret_cast<const unsigned char *>(p0);
+  t_hint_ptr[1] = reinterpret_cast<const unsigned char *>(p1);
+  t_hint_bytes[0] = p0 ? (unsigned)bytes0 : 0;
+  t_hint_bytes[1] = p1 ? (unsigned)bytes1 : 0;
+  return AB200_OK;
+}
+namespace ab200 {
 
 static int gemv_f32_dispatch(GemvParams p, int M, cudaStream_t s) {
   for (int m0 = 0; m0 < M; m0 += 2) {

@@ -3,9 +3,12 @@
 // Why warp MMA: on sm_100 the integer/logic pipe and the FP16 pipe both issue at half rate, so a
 // GEMV that multiplies on the scalar pipes (w4a16_gemv.cu, ~23 instructions per packed word)
 // saturates instruction issue near 45% of HBM bandwidth.  Here every dequantised nibble goes
-// through `mma.sync.m16n8k16` (fp16 x fp16 -> fp32): the scalar pipes only unpack (1 SHF + 4 LOP3
-// per word, 0x6400 fp16 magic) and remove the zero-point (4 HSUB2/HFMA2 per word), independent
-// of the batch size.  The weights are the A operand (16 output columns x 16 k), the activations
+// through `mma.sync.m16n8k16` (fp16 x fp16 -> fp32) as a raw bit pattern: `w & 0x000F000F` is the
+// pair of fp16 subnormals (q * 2^-24), `w & 0x00F000F0` the pair (16q * 2^-24), so the scalar pipes
+// only shift and mask (1 SHF + 4 LOP3 per word, nothing on the FP16 pipe), independent of the
+// batch size.  The matching x values are stored divided by 16 for the high nibbles, the
+// zero-point enters as the accumulator seed -8 * sum(x) * 2^-24 per scale group, and the fp32 sums
+// are multiplied by 2^24 once at the end; products are exact in the fp32 accumulators.  The weights are the A operand (16 output columns x 16 k), the activations
 // the B operand (16 k x 8 batch rows); batch rows beyond M read a zero block.
 //
 // Data path: unchanged HBM layout (qweight int32 [K/8, N]).  A warp owns 32 columns; lane
@@ -79,7 +82,8 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
   __half *xs = reinterpret_cast<__half *>(smem_raw + 256);
   float *red = reinterpret_cast<float *>(smem_raw + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));  // [WK][M][128]
   float *part = red + MMA_WK * M * TILE_N;                                                                    // [M][128]
-  const unsigned char *ring_p = reinterpret_cast<const unsigned char *>(part + M * TILE_N) + warp * (DEPTH * SLOT_BYTES) + lane * 16;
+  float *corr = part + M * TILE_N;  // [fold units of this slice][MB]: -8 * sum(x) * 2^-24 per fold unit and batch row
+  const unsigned char *ring_p = reinterpret_cast<const unsigned char *>(corr + (size_t)(p.xs_stride - XS_PAD) / 128 * NSC * MB) + warp * (DEPTH * SLOT_BYTES) + lane * 16;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_p);
 
   pdl_launch_dependents();
@@ -131,18 +135,41 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
   pdl_wait();  // x (and a residual output) may come from the kernel before this one
 
   // ---- prologue: this CTA's slice of x, permuted per packed row to (x0,x4)(x1,x5)(x2,x6)(x3,x7) ---------
+  // The nibbles enter the MMA as raw fp16 bit patterns (subnormals q * 2^-24; the high nibble of a
+  // byte is 16q * 2^-24), so the x values that meet high nibbles - words .y and .w of a permuted
+  // row - are stored divided by 16, and the zero-point becomes -8 * sum(x) per fold unit
+  // (SPG * 32 k), which seeds the MMA accumulators.
   const int rows = kslice / 8;
+  constexpr int FOLD_ROWS = SPG * 4;  // packed rows per fold unit (4, 8 or 16 lanes of a warp)
+  auto stage_row = [&](uint4 o, int m, int r, bool valid) {
+    const float2 f0 = __half22float2(u2h2(o.x)), f1 = __half22float2(u2h2(o.y)), f2 = __half22float2(u2h2(o.z)), f3 = __half22float2(u2h2(o.w));
+    float sx = valid ? ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y)) : 0.f;
+#pragma unroll
+    for (int off = FOLD_ROWS / 2; off > 0; off >>= 1) sx += __shfl_xor_sync(0xffffffffu, sx, off);
+    if (valid) {
+      uint4 q = permute_row(o);
+      const __half2 c16th = u2h2(0x2C002C00u);
+      q.y = h22u(__hmul2(u2h2(q.y), c16th));
+      q.w = h22u(__hmul2(u2h2(q.w), c16th));
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = q;
+      if (r % FOLD_ROWS == 0) corr[(r / FOLD_ROWS) * MB + m] = sx * (-8.0f * 5.9604644775390625e-8f);
+    }
+  };
+  for (int i = threadIdx.x; i < (be - bb) * NSC * (MB - M); i += MMA_THREADS)  // batch rows beyond M: zero seed
+    corr[(i / (MB - M)) * MB + M + i % (MB - M)] = 0.f;
+  const int stage_n = (M * rows + 31) & ~31;
   if (PRO == PRO_PLAIN) {
     const __half *xg = reinterpret_cast<const __half *>(p.x);
-    for (int i = threadIdx.x; i < M * rows; i += MMA_THREADS) {
-      const int m = i / rows, r = i - m * rows;
-      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) =
-          permute_row(*reinterpret_cast<const uint4 *>(xg + (size_t)m * K + k_begin + r * 8));
+    for (int i = threadIdx.x; i < stage_n; i += MMA_THREADS) {
+      const bool valid = i < M * rows;
+      const int m = valid ? i / rows : 0, r = valid ? i - m * rows : 0;
+      stage_row(*reinterpret_cast<const uint4 *>(xg + (size_t)m * K + k_begin + r * 8), m, r, valid);
     }
   } else if (PRO == PRO_SILU_MUL) {
     const __half *xg = reinterpret_cast<const __half *>(p.x);
-    for (int i = threadIdx.x; i < M * rows; i += MMA_THREADS) {
-      const int m = i / rows, r = i - m * rows;
+    for (int i = threadIdx.x; i < stage_n; i += MMA_THREADS) {
+      const bool valid = i < M * rows;
+      const int m = valid ? i / rows : 0, r = valid ? i - m * rows : 0;
       const uint4 gv = *reinterpret_cast<const uint4 *>(xg + (size_t)m * 2 * K + k_begin + r * 8);
       const uint4 uv = *reinterpret_cast<const uint4 *>(xg + (size_t)m * 2 * K + K + k_begin + r * 8);
       const uint32_t ga[4] = {gv.x, gv.y, gv.z, gv.w}, ua[4] = {uv.x, uv.y, uv.z, uv.w};
@@ -152,11 +179,12 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
         const float2 gf = __half22float2(u2h2(ga[j])), uf = __half22float2(u2h2(ua[j]));
         o[j] = h22u(__floats2half2_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y));
       }
-      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute_row(make_uint4(o[0], o[1], o[2], o[3]));
+      stage_row(make_uint4(o[0], o[1], o[2], o[3]), m, r, valid);
     }
   } else {  // RMSNorm of the fp32 row: every CTA recomputes the row's sum of squares (16 KiB from L2 at K = 4096)
     const float *xg = reinterpret_cast<const float *>(p.x);
     const int rowsK = K / 8;
+    const int rows_pad = (rows + 31) & ~31;
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
       for (int r = threadIdx.x; r < rowsK; r += MMA_THREADS) {
@@ -171,7 +199,9 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
       tot = warp_sum(tot);
       __syncthreads();
       const float rs = rsqrtf(tot * (1.0f / (float)K) + p.eps);
-      for (int r = threadIdx.x; r < rows; r += MMA_THREADS) {
+      for (int r0 = threadIdx.x; r0 < rows_pad; r0 += MMA_THREADS) {
+        const bool valid = r0 < rows;
+        const int r = valid ? r0 : 0;
         const float *xr = xg + (size_t)m * K + k_begin + r * 8;
         const float4 a = *reinterpret_cast<const float4 *>(xr), b = *reinterpret_cast<const float4 *>(xr + 4);
         const uint4 wv = *reinterpret_cast<const uint4 *>(p.norm_w + k_begin + r * 8);
@@ -182,7 +212,7 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
         o.y = h22u(__floats2half2_rn(a.z * rs * w1.x, a.w * rs * w1.y));
         o.z = h22u(__floats2half2_rn(b.x * rs * w2.x, b.y * rs * w2.y));
         o.w = h22u(__floats2half2_rn(b.z * rs * w3.x, b.w * rs * w3.y));
-        *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute_row(o);
+        stage_row(o, m, r, valid);
       }
     }
   }
@@ -216,6 +246,9 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) xp[nb] = smem_raw + (xa[nb] - zero_base);
 
+  // accumulator seeds of this lane's batch rows 2t, 2t+1 (per B-fragment set), first block of this warp
+  const float *cp = corr + wk * NSC * MB + 2 * t;
+
   auto compute_block = [&](int slot) {
     const unsigned char *src = ring_p + slot * SLOT_BYTES;
     float d[NB][2][4];
@@ -227,11 +260,14 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
     for (int s = 0; s < BLK_STEPS; ++s) {
       if (s % SPG == 0) {
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
+        for (int nb = 0; nb < NB; ++nb) {
+          const float2 seed = *reinterpret_cast<const float2 *>(cp + (s / SPG) * MB + nb * 8);
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) d[nb][j][i] = 0.f;
+          for (int j = 0; j < 2; ++j) {
+            d[nb][j][0] = d[nb][j][2] = seed.x;
+            d[nb][j][1] = d[nb][j][3] = seed.y;
+          }
+        }
       }
       const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
       uint4 xc[NB];
@@ -245,7 +281,7 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         uint32_t lo[4], hi[4];
-        unpack_pair(wr[2 * j], wr[2 * j + 1], lo, hi);
+        unpack_pair_raw(wr[2 * j], wr[2 * j + 1], lo, hi);
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
           mma16816p(d[nb][j], lo[0], lo[1], lo[2], lo[3], xc[nb].x, xc[nb].y);
@@ -269,6 +305,7 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
     }
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) xp[nb] += x_adv[nb];
+    cp += MMA_WK * NSC * MB;
   };
 
   for (int i0 = 0; i0 < nblk; i0 += DEPTH) {
@@ -293,7 +330,7 @@ __global__ void __launch_bounds__(MMA_THREADS) w4a16_gemv_mma_kernel(MmaGemvPara
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int m = nb * 8 + 2 * t + (i & 1);
-        if (m < M) red[(wk * M + m) * TILE_N + wn * 32 + g * 4 + 2 * j + (i >> 1)] = col_ok ? facc[nb][j][i] : 0.f;
+        if (m < M) red[(wk * M + m) * TILE_N + wn * 32 + g * 4 + 2 * j + (i >> 1)] = col_ok ? facc[nb][j][i] * 16777216.0f : 0.f;
       }
   __syncthreads();
   for (int i = threadIdx.x; i < M * TILE_N; i += MMA_THREADS) {
@@ -346,7 +383,7 @@ static int launch_mma(Kern kern, MmaGemvParams p, int depth, cudaStream_t stream
   auto smem_for = [&](int c) {
     const int blocks_max = (p.blocks + c - 1) / c;
     return 256 + (((size_t)p.M * (blocks_max * 128 + XS_PAD) * 2 + 15) & ~(size_t)15) + (size_t)(MMA_WK + 1) * p.M * TILE_N * sizeof(float) +
-           ring_bytes;
+           (size_t)blocks_max * 4 * 16 * sizeof(float) /* seeds: <= 4 fold units per block x 16 batch rows */ + ring_bytes;
   };
   while (smem_for(cs) > 200 * 1024 && cs < 8) cs *= 2;
   const size_t smem = smem_for(cs);

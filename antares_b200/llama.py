@@ -112,7 +112,7 @@ class LlamaInt4Decoder:
       all_reduce_sum_(t_f32)  and  all_gather_into(out, t)   (see parallel.py).
     """
 
-    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024):
+    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0):
         assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
         self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         self.hl = cfg.n_heads // world            # local heads
@@ -152,6 +152,11 @@ class LlamaInt4Decoder:
         self.att_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
         self.launches_per_step = 0
+        self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
+        self._plist = []
+        for w in self.layers:
+            for k in ("vqk", "o", "gu", "down"):
+                self._plist.append((w[k + "_q"], w[k + "_s"]))
         self._pin_in = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
 
@@ -160,6 +165,11 @@ class LlamaInt4Decoder:
         """One fused W4A16 projection launch (prologue 0 plain / 1 RMSNorm of the fp32 residual /
         2 SiLU(gate)*up; epilogue 0 fp16 / 1 residual += / 2 fp32 partial)."""
         K, N = q.shape[0] * 8, q.shape[1]
+        if self.prefetch == 1:
+            # the projection kernel itself pulls the NEXT projection's weights into L2 while it streams
+            nq, ns = self._plist[(self._pi + 1) % len(self._plist)]
+            call("ab200_w4a16_gemv_prefetch_hint", nq.data_ptr(), nq.numel() * 4, ns.data_ptr(), ns.numel() * 2)
+            self._pi += 1
         call("ab200_w4a16_gemv_fused", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
              q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, 0, 0, self._st)
         self._n += 1
@@ -182,6 +192,7 @@ class LlamaInt4Decoder:
         cfg = self.cfg
         self._st = torch.cuda.current_stream().cuda_stream
         self._n = 0
+        self._pi = 0
         st = self._st
         call("ab200_embed_lookup", self.embed.data_ptr(), self.token.data_ptr(), self.x.data_ptr(), cfg.dim, cfg.vocab, st)
         self._n += 1

@@ -215,6 +215,12 @@ int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, in
 int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
                       int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
 
+/* One-shot hint for the calling thread's NEXT fp16 ab200_w4a16_gemv* call: while that kernel
+ * streams its own weights, one thread per CTA also asks for the two byte ranges (normally the
+ * following projection's qweight and scales) to be pulled into L2, so HBM stays busy across the
+ * kernel boundary (measured neutral on B200 for the decode step; off by default there).  Results are unaffected.  Either pointer may be NULL.  No reference counterpart. */
+int ab200_w4a16_gemv_prefetch_hint(const void *p0, size_t bytes0, const void *p1, size_t bytes1);
+
 /* ---- tensor-parallel exchange over NVLink peer memory -----------------------------------------
  * The reference's only collectives are NCCL calls inside its TensorFlow plugin
  * (frameworks/tensorflow/communicate_ops.cc:65-99 bootstrap, :191 ncclAllReduce); its Llama
