@@ -33,9 +33,10 @@ int *kernel_error_ptr() {
   return cached[dev];
 }
 
-static bool g_pdl = false;
-bool pdl_enabled() { return g_pdl; }
-void pdl_set(bool on) { g_pdl = on; }
+static int g_pdl = 1;  // 0 off, 1 dependents released at kernel start, 2 GEMVs release them after their streaming loop
+bool pdl_enabled() { return g_pdl != 0; }
+int pdl_mode() { return g_pdl; }
+void pdl_set(int mode) { g_pdl = mode; }
 
 int sm_count() {
   static int cached[64] = {0};

@@ -42,7 +42,8 @@ int *kernel_error_ptr();  // device address of the status word that ab200_kernel
 // touching data an earlier kernel produced.
 void comm_set_wait_polls(unsigned polls);
 bool pdl_enabled();
-void pdl_set(bool on);
+int pdl_mode();
+void pdl_set(int mode);
 
 // Launch helper: <<<grid, block, smem, stream>>> plus the PDL attribute when enabled.
 template <typename... KArgs, typename... Args>

@@ -43,6 +43,7 @@ struct GemvParams {
   // L2 prefetch hint: up to two byte ranges (the next projection's packed weights and scales)
   const unsigned char *pf[2] = {nullptr, nullptr};
   unsigned pf_bytes[2] = {0, 0};
+  int pdl_late = 0;  // release the dependent kernel after the streaming loop instead of at the start
 };
 
 constexpr unsigned PF_CHUNK = 16 * 1024;
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     else sp = scol + (size_t)((u_load * UNIT_K) / p.group) * p.N;
   };
 
-  pdl_launch_dependents();
+  if (!p.pdl_late) pdl_launch_dependents();
   // the first NBUF units of this warp are on their way before x is staged
 #pragma unroll
   for (int b = 0; b < NBUF; ++b)
@@ -240,6 +241,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     }
   }
 
+  if (p.pdl_late) pdl_launch_dependents();
   reduce_and_store<M, EPI, GEMV_THREADS, GEMV_WARPS>(facc, red, part, p.out, p.N, tile * TILE_N);
 }
 
@@ -248,6 +250,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 // IR statement 2; products accumulate in fp32.
 template <int M>
 __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams p) {
+  pdl_launch_dependents();
+  pdl_wait();  // this variant has no preamble worth overlapping: wait first
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned cs = cluster.num_blocks(), krank = cluster.block_rank();
@@ -325,6 +329,7 @@ static int launch_gemv(Kern kern, GemvParams p, int M, int elt, cudaStream_t str
   const int cs = pick_cluster(tiles, p.units);
   const int kslice_max = ((p.units + cs - 1) / cs) * UNIT_K;
   p.xs_stride = kslice_max;
+  p.pdl_late = pdl_mode() == 2;
   size_t smem = (((size_t)M * kslice_max * elt + 15) & ~(size_t)15) +
                 (size_t)(GEMV_WARPS + 1) * M * TILE_N * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: K slice of %d values x M=%d does not fit shared memory", kslice_max, M);

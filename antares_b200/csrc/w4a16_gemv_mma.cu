@@ -454,7 +454,8 @@ int gemv_tuning_set(const char *name, int value) {
     if (value < 1) return fail(AB200_EINVAL, "comm_wait_polls must be positive");
     comm_set_wait_polls((unsigned)value);
   } else if (!strcmp(name, "pdl")) {
-    pdl_set(value != 0);
+    if (value < 0 || value > 2) return fail(AB200_EINVAL, "pdl must be 0 (off), 1 (release dependents at kernel start) or 2 (GEMVs release them after streaming)");
+    pdl_set(value);
   } else if (!strcmp(name, "gemv_depth")) {
     if (value != 0 && (value < 2 || value > 4)) return fail(AB200_EINVAL, "gemv_depth must be 0 or 2..4");
     g_tune.depth = value;

@@ -330,6 +330,9 @@ def run_ours(args):
     if world > 1:
         comm = parallel.TorchComm() if args.comm == "nccl" else parallel.PushComm(dev, 4096)
     K, W = args.steps, max(3, args.warmup)
+    if args.pdl >= 0:
+        from antares_b200 import ops as _ops
+        _ops.set_option("pdl", args.pdl)
     cfg = LlamaConfig(max_seq=N_PROMPT + W + K + 8)
     dec = LlamaInt4Decoder(cfg, dev, rank=rank, world=world, comm=comm, max_tokens=N_PROMPT + W + K + 8,
                            prefetch=args.prefetch)
@@ -419,6 +422,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the operator-level figures (prefill GEMM, GEMV set)")
+    ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 release dependents at kernel start, 2 after the GEMV streaming loop")
     ap.add_argument("--prefetch", type=int, default=0, help="1: every projection kernel also pulls the next one's weights into L2 (measured neutral)")
     ap.add_argument("--comm", default="push", choices=["push", "nccl"], help="all-reduce of row-parallel partials: one-shot NVLink push kernel or NCCL")
     args = ap.parse_args()

@@ -51,8 +51,10 @@ int ab200_kernel_status(int *status_host);
  * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA),
  * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel).
  * "comm_wait_polls": polls after which the push all-reduce gives up waiting for a peer.
- * "pdl" (0/1): launch kernels with programmatic dependent launch so that a kernel's weight
- * prefetch overlaps the tail of its predecessor in the stream.  Process-wide; host call. */
+ * "pdl" (0 off, 1 default, 2): launch kernels with programmatic dependent launch so that a
+ * kernel's weight prefetch overlaps the tail of its predecessor in the stream; every such kernel
+ * executes griddepcontrol.wait before it touches anything an earlier kernel wrote.  1 releases
+ * the dependent kernel at kernel start, 2 after the GEMV's streaming loop.  Process-wide; host call. */
 int ab200_set_option(const char *name, int value);
 
 /* Device property probe; replaces engine/cuda_properties.cc:35-52 (which prints

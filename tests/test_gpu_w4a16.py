@@ -216,3 +216,37 @@ def test_prefill_gemm_config3_full_size(cuda):
     lin = y[:1024].float() * 0.5 + y[1024:].float()
     assert (y2.float() - lin).abs().max() <= TOL * lin.abs().max()
     assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_dependent_chain_is_identical_under_programmatic_launch(cuda, impl):
+    """A chain in which each GEMV consumes the one before it (the shape of a decode layer) gives
+    bitwise the same result with programmatic dependent launch off, early and late: no kernel
+    reads its input before the producer has finished."""
+    K = 4096
+    rng = np.random.default_rng(77)
+    ws = [packing.synth_w4(K, K, 80 + i) for i in range(6)]
+    dws = [(_dev(q, cuda), _dev(s, cuda)) for q, s in ws]
+    x0 = _dev((rng.standard_normal((1, K)) * 0.5).astype(np.float16), cuda)
+    results = []
+    ops.set_option("gemv_impl", impl)
+    try:
+        for mode in (0, 1, 2):
+            ops.set_option("pdl", mode)
+            bufs = [torch.empty((1, K), dtype=torch.float16, device=cuda) for _ in range(2)]
+            for rep in range(3):
+                cur = x0
+                for i, (q, s) in enumerate(dws):
+                    out = bufs[i % 2]
+                    ops.w4a16_gemv(cur, q, s, out)
+                    # keep magnitudes bounded so that the chain stays in fp16 range
+                    cur = out
+                    if i % 2 == 1:
+                        cur = (out * (1.0 / 64)).to(torch.float16)
+            torch.cuda.synchronize()
+            results.append(cur.clone())
+    finally:
+        ops.set_option("pdl", 1)
+        ops.set_option("gemv_impl", 0)
+    assert torch.isfinite(results[0].float()).all()
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
