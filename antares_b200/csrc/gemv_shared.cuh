@@ -149,6 +149,11 @@ int gemv_mma_dispatch(const void *x, int pro, const __half *norm_w, float eps, c
 int gemv_tuning_set(const char *name, int value);
 int gemv_tuning_impl();
 
+// TMA-ring variant (w4a16_gemv_tma.cu)
+bool gemv_tma_eligible(int dtype, int M, int K, int N, int group);
+int gemv_tma_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                      int K, int N, int group, int epi, cudaStream_t s, bool *handled);
+
 // persistent balanced variant (w4a16_gemv_persist.cu)
 enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 constexpr size_t PERSIST_COUNTER_BYTES = 64 * 1024;  // counters live at the start of the scratch: up to 16384 column tiles

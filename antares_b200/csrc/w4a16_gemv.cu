@@ -450,6 +450,11 @@ static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps
     }
     return gemv_persist_dispatch(x, norm_w, eps, qw, scales, out, M, K, N, group, pro, epi, scratch, s);
   }
+  if (impl == 4) {
+    bool handled = false;
+    const int rc = gemv_tma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
+    if (rc || handled) return rc;
+  }
   if ((impl == 2 || (impl == 0 && M > 2)) && gemv_mma_eligible(AB200_F16, M, K, N))
     return gemv_mma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s);
   GemvParams p{x, qw, scales, out, K, N, group, K / UNIT_K, 0};

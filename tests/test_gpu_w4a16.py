@@ -139,7 +139,7 @@ def test_errors_are_raised_not_fallen_back(cuda):
         ops.w4a16_gemv(_dev(packing.synth_x(17, 256, 2), cuda), _dev(qw, cuda), _dev(sc, cuda))
 
 
-@pytest.mark.parametrize("impl", [1, 2, 3])
+@pytest.mark.parametrize("impl", [1, 2, 3, 4])
 @pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (3, 11008, 4096), (1, 4096, 22016), (9, 1408, 2752), (2, 256, 36)])
 def test_every_gemv_variant_matches_oracle(cuda, impl, M, K, N):
     """The scalar-pipe, cluster warp-MMA and persistent warp-MMA kernels compute the same contraction."""
@@ -218,7 +218,7 @@ def test_prefill_gemm_config3_full_size(cuda):
     assert ops.kernel_status() == 0
 
 
-@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("impl", [1, 2, 4])
 def test_dependent_chain_is_identical_under_programmatic_launch(cuda, impl):
     """A chain in which each GEMV consumes the one before it (the shape of a decode layer) gives
     bitwise the same result with programmatic dependent launch off, early and late: no kernel
