@@ -117,7 +117,15 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
-  // (x0,x4)(x1,x5)(x2,x6)(x3,x7): the pairing the nibble unpack produces.
+  // (x0,x4)(x1,x5)(x2,x6)(x3,x7): the pairing the nibble masks produce.
+  //
+  // The nibbles meet x as raw fp16 bit patterns: `w & 0x000F000F` is the pair of subnormals
+  // (q * 2^-24), `w & 0x00F000F0` the pair (16q * 2^-24).  So that the products stay in fp16's
+  // normal range, each batch row of the slice is scaled by a power of two 2^e chosen from its
+  // largest magnitude (|x| * 2^e < 2^15); the words that meet high nibbles carry another 1/16.
+  // The zero-point becomes 8 * sum(x * 2^e) * 2^-24 per unit, subtracted in fp32, and the fp32
+  // row sums are multiplied by 2^(24 - e) before the cross-warp reduction.  Exact powers of two
+  // throughout: the only roundings are those of the fp16 product chain, as before.
   auto permute = [](uint4 v) {
     uint4 o;
     o.x = __byte_perm(v.x, v.z, 0x5410);
@@ -126,13 +134,29 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     o.w = __byte_perm(v.y, v.w, 0x7632);
     return o;
   };
+  __shared__ unsigned sh_max[M][GEMV_WARPS];
+  __shared__ float sh_back[M];  // 2^(24 - e) per batch row
+  float *corr = part + M * TILE_N;  // [M][units of the slice]: 8 * 2^-24 * sum over the unit of x * 2^e
   const int rows = kslice / 8;
+  const int n_units = u_end - u_begin;
+  unsigned mx[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) mx[m] = 0u;
+  auto track = [&](uint4 v, int m) {
+    const unsigned a = (v.x & 0x7FFF7FFFu), b = (v.y & 0x7FFF7FFFu), c = (v.z & 0x7FFF7FFFu), d = (v.w & 0x7FFF7FFFu);
+    unsigned t = max(max(a & 0xFFFFu, a >> 16), max(b & 0xFFFFu, b >> 16));
+    t = max(t, max(max(c & 0xFFFFu, c >> 16), max(d & 0xFFFFu, d >> 16)));
+#pragma unroll
+    for (int mm = 0; mm < M; ++mm)
+      if (mm == m) mx[mm] = max(mx[mm], t);
+  };
   if (PRO == PRO_PLAIN) {
     const __half *xg = reinterpret_cast<const __half *>(p.x);
     for (int i = threadIdx.x; i < M * rows; i += GEMV_THREADS) {
       const int m = i / rows, r = i % rows;
-      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) =
-          permute(*reinterpret_cast<const uint4 *>(xg + (size_t)m * p.K + k_begin + r * 8));
+      const uint4 v = *reinterpret_cast<const uint4 *>(xg + (size_t)m * p.K + k_begin + r * 8);
+      track(v, m);
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(v);
     }
   } else if (PRO == PRO_SILU_MUL) {
     const __half *xg = reinterpret_cast<const __half *>(p.x);
@@ -147,7 +171,9 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
         const float2 gf = __half22float2(u2h2(ga[j])), uf = __half22float2(u2h2(ua[j]));
         o[j] = h22u(__floats2half2_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y));
       }
-      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(make_uint4(o[0], o[1], o[2], o[3]));
+      const uint4 v = make_uint4(o[0], o[1], o[2], o[3]);
+      track(v, m);
+      *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(v);
     }
   } else {
     __shared__ float sh_ss[GEMV_WARPS];
@@ -178,8 +204,59 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
         o.y = h22u(__floats2half2_rn(a.z * rs * w1.x, a.w * rs * w1.y));
         o.z = h22u(__floats2half2_rn(b.x * rs * w2.x, b.y * rs * w2.y));
         o.w = h22u(__floats2half2_rn(b.z * rs * w3.x, b.w * rs * w3.y));
+        track(o, m);
         *reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8) = permute(o);
       }
+    }
+  }
+  // largest |x| bit pattern per batch row -> exponent e
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const unsigned wm = __reduce_max_sync(0xffffffffu, mx[m]);
+    if (lane == 0) sh_max[m][warp] = wm;
+  }
+  __syncthreads();
+  float up[M];  // 2^e
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    unsigned t = 0u;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) t = max(t, sh_max[m][w]);
+    int E = (int)(t >> 10);          // biased fp16 exponent of the largest magnitude: |x| < 2^(E - 14)
+    if (E < 1) E = 1;                // all zero or subnormal
+    if (E > 30) E = 30;              // inf/nan rows: no scaling that helps
+    const int e = 29 - E;            // |x| * 2^e < 2^15
+    up[m] = __int_as_float((127 + e) << 23);
+    if (threadIdx.x == 0) sh_back[m] = __int_as_float((127 + 24 - e) << 23);
+  }
+  // second pass over the same elements (each thread rescales what it staged): x * 2^e, the
+  // high-nibble words another 1/16, and the per-unit sums (4 packed rows = 4 adjacent lanes)
+  {
+    const int n_pad = (M * rows + 31) & ~31;
+    for (int i = threadIdx.x; i < n_pad; i += GEMV_THREADS) {
+      const bool valid = i < M * rows;
+      const int m = valid ? i / rows : 0, r = valid ? i % rows : 0;
+      float f = 0.f;
+#pragma unroll
+      for (int mm = 0; mm < M; ++mm)
+        if (mm == m) f = up[mm];
+      uint4 *slot = reinterpret_cast<uint4 *>(xs + (size_t)m * xs_stride + r * 8);
+      float sx = 0.f;
+      if (valid) {
+        const uint4 v = *slot;
+        const float2 a = __half22float2(u2h2(v.x)), b = __half22float2(u2h2(v.y)), c = __half22float2(u2h2(v.z)), d = __half22float2(u2h2(v.w));
+        const float g = f * 0.0625f;
+        sx = ((a.x + a.y) + (b.x + b.y) + (c.x + c.y) + (d.x + d.y)) * f;
+        uint4 o;
+        o.x = h22u(__floats2half2_rn(a.x * f, a.y * f));
+        o.y = h22u(__floats2half2_rn(b.x * g, b.y * g));
+        o.z = h22u(__floats2half2_rn(c.x * f, c.y * f));
+        o.w = h22u(__floats2half2_rn(d.x * g, d.y * g));
+        *slot = o;
+      }
+      sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+      sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+      if (valid && (r & 3) == 0) corr[m * n_units + (r >> 2)] = sx * (8.0f * 5.9604644775390625e-8f);
     }
   }
   __syncthreads();
@@ -192,7 +269,9 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 
   const uint4 *xp = reinterpret_cast<const uint4 *>(xs) + warp * UNIT_ROWS;  // this warp's unit within the slice
   const unsigned xm_step = (unsigned)xs_stride / 8;                            // uint4 elements between batch rows
+  const float *cp = corr + warp;                                               // this warp's unit correction
   auto compute_unit = [&](int b) {
+    constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
     __half2 hacc[M][4];
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -206,27 +285,30 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
       const uint32_t wr[4] = {wbuf[b][r].x, wbuf[b][r].y, wbuf[b][r].z, wbuf[b][r].w};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        __half2 v[4];
-        unpack8(wr[c], v);
+        const uint32_t w = wr[c], w8 = w >> 8;
+        const __half2 v0 = u2h2(w & LO), v1 = u2h2(w & HI), v2 = u2h2(w8 & LO), v3 = u2h2(w8 & HI);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          hacc[m][c] = __hfma2(v[0], u2h2(xr[m].x), hacc[m][c]);
-          hacc[m][c] = __hfma2(v[1], u2h2(xr[m].y), hacc[m][c]);
-          hacc[m][c] = __hfma2(v[2], u2h2(xr[m].z), hacc[m][c]);
-          hacc[m][c] = __hfma2(v[3], u2h2(xr[m].w), hacc[m][c]);
+          hacc[m][c] = __hfma2(v0, u2h2(xr[m].x), hacc[m][c]);
+          hacc[m][c] = __hfma2(v1, u2h2(xr[m].y), hacc[m][c]);
+          hacc[m][c] = __hfma2(v2, u2h2(xr[m].z), hacc[m][c]);
+          hacc[m][c] = __hfma2(v3, u2h2(xr[m].w), hacc[m][c]);
         }
       }
     }
     const float2 s01 = __half22float2(u2h2(sbuf[b].x)), s23 = __half22float2(u2h2(sbuf[b].y));
     const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
 #pragma unroll
-    for (int m = 0; m < M; ++m)
+    for (int m = 0; m < M; ++m) {
+      const float zp = cp[m * n_units];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float2 f = __half22float2(hacc[m][c]);
-        facc[m][c] = fmaf(sc[c], f.x + f.y, facc[m][c]);
+        facc[m][c] = fmaf(sc[c], (f.x + f.y) - zp, facc[m][c]);
       }
+    }
     xp += UNIT_ROWS * GEMV_WARPS;
+    cp += GEMV_WARPS;
   };
 
   // NBUF-deep software pipeline over this warp's units: a buffer is refilled as soon as it is consumed.
@@ -242,6 +324,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   }
 
   if (p.pdl_late) pdl_launch_dependents();
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const float back = sh_back[m];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) facc[m][c] *= back;
+  }
   reduce_and_store<M, EPI, GEMV_THREADS, GEMV_WARPS>(facc, red, part, p.out, p.N, tile * TILE_N);
 }
 
@@ -331,7 +419,7 @@ static int launch_gemv(Kern kern, GemvParams p, int M, int elt, cudaStream_t str
   p.xs_stride = kslice_max;
   p.pdl_late = pdl_mode() == 2;
   size_t smem = (((size_t)M * kslice_max * elt + 15) & ~(size_t)15) +
-                (size_t)(GEMV_WARPS + 1) * M * TILE_N * sizeof(float);
+                (size_t)(GEMV_WARPS + 1) * M * TILE_N * sizeof(float) + (size_t)M * (kslice_max / UNIT_K) * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: K slice of %d values x M=%d does not fit shared memory", kslice_max, M);
   // Raising the limit is idempotent; doing it per launch keeps the library stateless across devices.
   if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
