@@ -97,7 +97,14 @@ __device__ __forceinline__ void unpack_pair_raw(uint32_t w0, uint32_t w1, uint32
 // Cross-warp, then cross-CTA (cluster) reduction of per-thread fp32 partials, and the epilogue.
 // Warps 0..NWARPS-1 hold partials (facc[m][c] for columns lane*4+c); every thread of the CTA
 // must call this (it contains CTA and cluster barriers).  The order of every sum is fixed, so
-// results are bitwise repeatable.  red: [NWARPS][M][128] floats, part: [M][128] floats.
+// results are bitwise repeatable.  red: [NWARPS][M][128] floats; part: M * 128 floats used as an
+// inbox [source rank][M][128 / cluster size].
+//
+// Push model: every CTA adds its warps' partials per column and STORES the sum into the inbox of
+// the CTA that owns the column (rank r owns columns [r * 128/cs, (r+1) * 128/cs)); one cluster
+// barrier later each owner adds the cs entries of its inbox in rank order and writes the result.
+// Remote stores do not wait for a round trip and nothing reads a peer's memory after the
+// barrier, so no second barrier is needed before exit.
 template <int M, int EPI, int NTHREADS, int NWARPS>
 __device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red, float *part, void *out, int N, int tile_n0) {
   namespace cg = cooperative_groups;
@@ -108,26 +115,24 @@ __device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red
       *reinterpret_cast<float4 *>(&red[(warp * M + m) * TILE_N + lane * 4]) = make_float4(facc[m][0], facc[m][1], facc[m][2], facc[m][3]);
   }
   __syncthreads();
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
+  const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
   for (int i = threadIdx.x; i < M * TILE_N; i += NTHREADS) {
     const int m = i / TILE_N, c = i % TILE_N;
     float s = 0.f;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) s += red[(w * M + m) * TILE_N + c];
-    part[i] = s;
+    const int owner = c / cols_per, cc = c - owner * cols_per;
+    float *inbox = (cs > 1) ? cluster.map_shared_rank(part, owner) : part;
+    inbox[(rank * M + m) * cols_per + cc] = s;
   }
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned cs = cluster.num_blocks();
   if (cs > 1) cluster.sync(); else __syncthreads();
-  const unsigned rank = cluster.block_rank();
-  const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
   for (int i = threadIdx.x; i < M * cols_per; i += NTHREADS) {
-    const int m = i / cols_per, c = rank * cols_per + i % cols_per;
+    const int m = i / cols_per, cc = i - m * cols_per;
     float s = 0.f;
-    for (unsigned r = 0; r < cs; ++r) {
-      const float *remote = (cs > 1) ? cluster.map_shared_rank(part, r) : part;
-      s += remote[m * TILE_N + c];
-    }
-    const int n = tile_n0 + c;
+    for (unsigned r = 0; r < cs; ++r) s += part[(r * M + m) * cols_per + cc];
+    const int n = tile_n0 + rank * cols_per + cc;
     if (n < N) {
       if (EPI == EPI_STORE) {
         reinterpret_cast<__half *>(out)[(size_t)m * N + n] = __float2half_rn(s);
@@ -139,7 +144,6 @@ __device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red
       }
     }
   }
-  if (cs > 1) cluster.sync();  // keep `part` alive until every peer has read it
 }
 
 // warp-MMA variant (w4a16_gemv_mma.cu)
