@@ -120,6 +120,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *
 // distributed shared memory.  Every CTA rotates q and the new k of its head itself (128 values);
 // the CTA that owns row `pos` writes the rotated k and v into the cache and uses its own copy, so
 // nothing is read back from global memory inside the kernel.
+// Latency: the position counter and up to 64 cache rows per CTA are fetched into registers before
+// griddepcontrol.wait, i.e. while the projection that produces q/k/v is still finishing.  That is
+// why the position counter and the cache rows below it must not be written by the kernel that
+// immediately precedes this one in the stream (in a decode step they date from earlier steps).
 struct AttnFusedParams {
   const __half *vqk;      // [3 * H * D]: V | Q | K of the current token
   const float *inv_freq;  // [D/2 or D]
@@ -132,6 +136,8 @@ struct AttnFusedParams {
   int rows_per_cta;       // ceil(max_seq / SPLITS): capacity of the score buffer
 };
 
+constexpr int ATT_PF = 4;  // cache rows per thread fetched before the current token's q/k/v exist
+
 __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedParams p) {
   namespace cg = cooperative_groups;
   extern __shared__ __align__(16) float att_smem[];
@@ -140,25 +146,44 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   const int h = blockIdx.x / splits;
   float *sc = att_smem;                      // [rows_per_cta] scores, then exp weights
   float *red = sc + p.rows_per_cta;          // [16][128] partial P.V
-  float *part = red + 16 * ATT_D;            // [128 + 2]: this CTA's o (un-normalised), max, sum
+  float *inbox = red + 16 * ATT_D;           // [splits][128/splits] weighted V, then [splits] max, [splits] sum
   __shared__ __align__(16) __half q_s[ATT_D], k_s[ATT_D], v_s[ATT_D];
   __shared__ float sh[32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int chunk = threadIdx.x & 15, sgroup = threadIdx.x >> 4;  // 16-byte chunk of a row; row group (16 rows per pass)
 
   pdl_launch_dependents();
-  pdl_wait();
+  // Everything up to the wait reads only what earlier steps left behind (the position counter and
+  // cache rows below it), so it overlaps the tail of the projection kernel that produces q/k/v.
   const int pos = *p.pos_dev;
   if (pos < 0 || pos >= p.max_seq) {  // out-of-range step: leave cache and output untouched (all CTAs agree)
     return;
   }
   const int S = pos + 1;
   const int HD = p.H * ATT_D;
+  const int n_local = (S - split + splits - 1) / splits;  // rows split, split+splits, ... < S
+  const __half *kh = p.kc + (size_t)h * ATT_D + chunk * 8;
+  const __half *vh = p.vc + (size_t)h * ATT_D + chunk * 8;
+  uint4 kreg[ATT_PF], vreg[ATT_PF];
+#pragma unroll
+  for (int j = 0; j < ATT_PF; ++j) {
+    const int i = sgroup + 16 * j;
+    const int s = split + i * splits;
+    kreg[j] = vreg[j] = make_uint4(0, 0, 0, 0);
+    if (i < n_local && s != pos) {
+      kreg[j] = ldg_stream_v4(kh + (size_t)s * p.kv_stride);
+      vreg[j] = ldg_stream_v4(vh + (size_t)s * p.kv_stride);
+    }
+  }
+  float freq = 0.f;
+  if (threadIdx.x < ATT_D / 2) freq = p.inv_freq[threadIdx.x];
+  pdl_wait();
 
   // rotate q and k of this head (rotate-half), keep v
   if (threadIdx.x < ATT_D / 2) {
     const int j = threadIdx.x;
     float sn, cs;
-    sincosf((float)pos * p.inv_freq[j], &sn, &cs);
+    sincosf((float)pos * freq, &sn, &cs);
     const __half *q = p.vqk + HD + (size_t)h * ATT_D, *k = p.vqk + 2 * HD + (size_t)h * ATT_D;
     const float qa = __half2float(q[j]), qb = __half2float(q[j + ATT_D / 2]);
     const float ka = __half2float(k[j]), kb = __half2float(k[j + ATT_D / 2]);
@@ -177,20 +202,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     reinterpret_cast<uint4 *>(p.vc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(v_s)[threadIdx.x];
   }
 
-  // scores of this CTA's rows: a half-warp per row
-  const int sub = lane & 15, hw = lane >> 4;
+  // scores of this CTA's rows: 16 lanes per row, row i = sgroup + 16 * pass
   float qf[8];
-  h8_to_f8(reinterpret_cast<const uint4 *>(q_s)[sub], qf);
-  const __half *kh = p.kc + (size_t)h * ATT_D + sub * 8;
-  const int n_local = (S - split + splits - 1) / splits;  // rows split, split+splits, ... < S
+  h8_to_f8(reinterpret_cast<const uint4 *>(q_s)[chunk], qf);
   float mx = -CUDART_INF_F;
-  for (int i0 = warp * 2; i0 < n_local; i0 += 2 * (ATT_THREADS / 32)) {
-    const int i = i0 + hw;
-    const int s = split + i * splits;
+  auto score_row = [&](int i, uint4 kv) {
     float dot = 0.f;
     if (i < n_local) {
       float kf[8];
-      const uint4 kv = (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[sub] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
       h8_to_f8(kv, kf);
 #pragma unroll
       for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
@@ -199,9 +218,24 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     if (i < n_local) {
       dot *= p.scale;
-      if (sub == 0) sc[i] = dot;
+      if (chunk == 0) sc[i] = dot;
       mx = fmaxf(mx, dot);
     }
+  };
+#pragma unroll
+  for (int j = 0; j < ATT_PF; ++j) {
+    const int i = sgroup + 16 * j;
+    if (16 * j < n_local) {  // uniform over the CTA
+      const int s = split + i * splits;
+      score_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[chunk] : kreg[j]);
+    }
+  }
+  for (int i0 = 16 * ATT_PF; i0 < n_local; i0 += 16) {
+    const int i = i0 + sgroup;
+    const int s = split + i * splits;
+    uint4 kv = make_uint4(0, 0, 0, 0);
+    if (i < n_local) kv = (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[chunk] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
+    score_row(i, kv);
   }
   mx = warp_max(mx);
   if (lane == 0) sh[warp] = mx;
@@ -211,7 +245,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   __syncthreads();
   float sum = 0.f;
   for (int i = threadIdx.x; i < n_local; i += ATT_THREADS) {
-    const float e = expf(sc[i] - mx);
+    const float e = __expf(sc[i] - mx);
     sc[i] = e;
     sum += e;
   }
@@ -221,52 +255,59 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   sum = (lane < ATT_THREADS / 32) ? sh[lane] : 0.f;
   sum = warp_sum(sum);
 
-  // partial P.V: 16 row groups x 16 chunks of 8 dims
-  const int dchunk = threadIdx.x & 15, sgroup = threadIdx.x >> 4;
+  // partial P.V with the same thread -> (row, chunk) mapping
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  const __half *vh = p.vc + (size_t)h * ATT_D + dchunk * 8;
-  for (int i = sgroup; i < n_local; i += 16) {
-    const int s = split + i * splits;
+  auto pv_row = [&](int i, uint4 vv) {
     float vf[8];
-    const uint4 vv = (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[dchunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride);
     h8_to_f8(vv, vf);
     const float ps = sc[i];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps, vf[j], acc[j]);
+  };
+#pragma unroll
+  for (int j = 0; j < ATT_PF; ++j) {
+    const int i = sgroup + 16 * j;
+    if (i < n_local) {
+      const int s = split + i * splits;
+      pv_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[chunk] : vreg[j]);
+    }
+  }
+  for (int i = 16 * ATT_PF + sgroup; i < n_local; i += 16) {
+    const int s = split + i * splits;
+    pv_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[chunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride));
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) red[sgroup * ATT_D + dchunk * 8 + j] = acc[j];
+  for (int j = 0; j < 8; ++j) red[sgroup * ATT_D + chunk * 8 + j] = acc[j];
   __syncthreads();
+  // merge across the head's CTAs, push model: CTA r stores its un-normalised output slice, max and
+  // sum into the inbox of the CTA that finalises those dims; one cluster barrier; local merge.
+  const int dims_per = ATT_D / splits;
   if (threadIdx.x < ATT_D) {
     float t = 0.f;
 #pragma unroll
     for (int gI = 0; gI < 16; ++gI) t += red[gI * ATT_D + threadIdx.x];
-    part[threadIdx.x] = t;
-  }
-  if (threadIdx.x == 0) {
-    part[ATT_D] = mx;
-    part[ATT_D + 1] = sum;
+    const int owner = threadIdx.x / dims_per, dd = threadIdx.x - owner * dims_per;
+    float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
+    dst[split * dims_per + dd] = t;
+  } else if (threadIdx.x < ATT_D + splits) {
+    const int owner = threadIdx.x - ATT_D;
+    float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
+    dst[ATT_D + split] = mx;
+    dst[ATT_D + splits + split] = sum;
   }
   if (splits > 1) cluster.sync(); else __syncthreads();
-  // merge: CTA `split` finalises dims [split*128/splits, ...)
-  const int dims_per = ATT_D / splits;
   if (threadIdx.x < dims_per) {
     const int d = split * dims_per + threadIdx.x;
     float gm = -CUDART_INF_F;
-    for (int r = 0; r < splits; ++r) {
-      const float *rp = (splits > 1) ? cluster.map_shared_rank(part, r) : part;
-      gm = fmaxf(gm, rp[ATT_D]);
-    }
+    for (int r = 0; r < splits; ++r) gm = fmaxf(gm, inbox[ATT_D + r]);
     float l = 0.f, o = 0.f;
     for (int r = 0; r < splits; ++r) {
-      const float *rp = (splits > 1) ? cluster.map_shared_rank(part, r) : part;
-      const float w = expf(rp[ATT_D] - gm);  // a CTA without rows has max -inf -> weight 0
-      l += rp[ATT_D + 1] * w;
-      o += rp[d] * w;
+      const float w = __expf(inbox[ATT_D + r] - gm);  // a CTA without rows has max -inf -> weight 0
+      l += inbox[ATT_D + splits + r] * w;
+      o += inbox[r * dims_per + threadIdx.x] * w;
     }
     p.out[(size_t)h * ATT_D + d] = __float2half_rn(o / l);
   }
-  if (splits > 1) cluster.sync();
 }
 
 // logits[n] = W[n, :] . x, W fp16 [N, K] row-major (the classifier matmul,
@@ -364,7 +405,7 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   while (splits < 8 && H * splits * 2 <= 2 * sm_count()) splits *= 2;  // up to ~2 CTAs per SM, at most 8 per head
   AttnFusedParams p{(const __half *)vqk_f16, inv_freq, pos_dev, (__half *)k_cache_f16, (__half *)v_cache_f16, (__half *)out_f16,
                     H, max_seq, kv_stride, scale, (max_seq + splits - 1) / splits};
-  const size_t smem = ((size_t)p.rows_per_cta + 16 * ATT_D + ATT_D + 2 + 2) * sizeof(float);
+  const size_t smem = ((size_t)p.rows_per_cta + 16 * ATT_D + ATT_D + 2 * 8) * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_fused: max_seq=%d exceeds the shared-memory score buffer", max_seq);
   if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};

@@ -198,7 +198,10 @@ int ab200_rope_kv_store(const void *vqk_f16, const float *inv_freq, const int32_
 
 /* The three calls above in one launch: splits vqk (V | Q | K), rotates Q and K at position
  * *pos_dev, stores K and V into cache row *pos_dev and attends over rows 0..*pos_dev (lines
- * 151-165).  Heads are split over several CTAs that merge through distributed shared memory. */
+ * 151-165).  Heads are split over several CTAs that merge through distributed shared memory.
+ * With programmatic dependent launch on (the default), *pos_dev and the cache rows below it are
+ * read before the preceding kernel in the stream has finished: they must come from earlier work
+ * (in a decode step they date from earlier steps), not from that kernel. */
 int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev,
                           void *k_cache_f16, void *v_cache_f16, void *out_f16, int H, int D,
                           long kv_stride, int max_seq, float scale, void *stream);
