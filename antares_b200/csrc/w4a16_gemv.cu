@@ -114,6 +114,25 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   for (int b = 0; b < NBUF; ++b)
     if (u_load < u_end) load_unit(b);
   if (threadIdx.x == GEMV_THREADS - 1) issue_prefetch_hint(p);
+
+  // Fast RMSNorm prologue (one batch row, slice of at most 256 packed rows): everything that only
+  // needs the constant norm weights happens before the wait - this thread's slice of them, and the
+  // largest |w| of the whole row, which bounds the normalised activations.
+  const int rows = kslice / 8;
+  const bool fast_rms = (M == 1) && (PRO == PRO_RMSNORM) && rows <= GEMV_THREADS;
+  __shared__ unsigned sh_wmax[GEMV_WARPS];
+  uint4 nw_slice = make_uint4(0, 0, 0, 0);
+  if (fast_rms) {
+    if ((int)threadIdx.x < rows) nw_slice = __ldg(reinterpret_cast<const uint4 *>(p.norm_w + k_begin) + threadIdx.x);
+    unsigned wm = 0u;
+    for (int r = threadIdx.x; r < p.K / 8; r += GEMV_THREADS) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.norm_w) + r);
+      const unsigned a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu, c = v.z & 0x7FFF7FFFu, d = v.w & 0x7FFF7FFFu;
+      wm = max(wm, max(max(max(a & 0xFFFFu, a >> 16), max(b & 0xFFFFu, b >> 16)), max(max(c & 0xFFFFu, c >> 16), max(d & 0xFFFFu, d >> 16))));
+    }
+    wm = __reduce_max_sync(0xffffffffu, wm);
+    if (lane == 0) sh_wmax[warp] = wm;
+  }
   pdl_wait();                      // x (and the output buffer) may come from the kernel before this one
 
   // Stage this CTA's slice of x into shared memory, permuted so that packed row r holds
@@ -137,8 +156,67 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   __shared__ unsigned sh_max[M][GEMV_WARPS];
   __shared__ float sh_back[M];  // 2^(24 - e) per batch row
   float *corr = part + M * TILE_N;  // [M][units of the slice]: 8 * 2^-24 * sum over the unit of x * 2^e
-  const int rows = kslice / 8;
   const int n_units = u_end - u_begin;
+  if (fast_rms) {
+    __shared__ float sh_ss1[GEMV_WARPS], sh_xm1[GEMV_WARPS];
+    const float *xg = reinterpret_cast<const float *>(p.x);
+    const bool valid = (int)threadIdx.x < rows;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (valid) {
+      a = *reinterpret_cast<const float4 *>(xg + k_begin + threadIdx.x * 8);
+      b = *reinterpret_cast<const float4 *>(xg + k_begin + threadIdx.x * 8 + 4);
+    }
+    float ss = 0.f, xm = 0.f;
+    for (int r = threadIdx.x; r < p.K / 8; r += GEMV_THREADS) {
+      const float4 c = *reinterpret_cast<const float4 *>(xg + r * 8), d = *reinterpret_cast<const float4 *>(xg + r * 8 + 4);
+      ss += c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w + d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w;
+      xm = fmaxf(fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w))),
+                 fmaxf(xm, fmaxf(fmaxf(fabsf(d.x), fabsf(d.y)), fmaxf(fabsf(d.z), fabsf(d.w)))));
+    }
+    ss = warp_sum(ss);
+    xm = warp_max(xm);
+    if (lane == 0) {
+      sh_ss1[warp] = ss;
+      sh_xm1[warp] = xm;
+    }
+    __syncthreads();
+    float tot = 0.f, xmx = 0.f;
+    unsigned wmx = 0u;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) {
+      tot += sh_ss1[w];
+      xmx = fmaxf(xmx, sh_xm1[w]);
+      wmx = max(wmx, sh_wmax[w]);
+    }
+    const float rs = rsqrtf(tot * (1.0f / (float)p.K) + p.eps);
+    const float bound = xmx * __half2float(__ushort_as_half((unsigned short)wmx)) * rs * 1.002f;  // >= every |x * rs * w|
+    int E = ((__float_as_int(bound) >> 23) & 255) - 112;  // fp16 biased exponent of the bound: |x| < 2^(E - 14)
+    if (E < 1) E = 1;
+    if (E > 30) E = 30;
+    const int e = 29 - E;
+    const float f = __int_as_float((127 + e) << 23), g = f * 0.0625f;
+    if (threadIdx.x == 0) sh_back[0] = __int_as_float((127 + 24 - e) << 23);
+    const float2 w0 = __half22float2(u2h2(nw_slice.x)), w1 = __half22float2(u2h2(nw_slice.y)), w2 = __half22float2(u2h2(nw_slice.z)),
+                 w3 = __half22float2(u2h2(nw_slice.w));
+    // normalised activations rounded to fp16 first (that is the operator's input), then scaled
+    const float2 o0 = __half22float2(__floats2half2_rn(a.x * rs * w0.x, a.y * rs * w0.y));
+    const float2 o1 = __half22float2(__floats2half2_rn(a.z * rs * w1.x, a.w * rs * w1.y));
+    const float2 o2 = __half22float2(__floats2half2_rn(b.x * rs * w2.x, b.y * rs * w2.y));
+    const float2 o3 = __half22float2(__floats2half2_rn(b.z * rs * w3.x, b.w * rs * w3.y));
+    float sx = valid ? ((o0.x + o0.y) + (o1.x + o1.y) + (o2.x + o2.y) + (o3.x + o3.y)) * f : 0.f;
+    sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+    sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+    if (valid) {
+      // natural order (x0,x1)(x2,x3)(x4,x5)(x6,x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7); odd k meet high nibbles
+      uint4 q;
+      q.x = h22u(__floats2half2_rn(o0.x * f, o2.x * f));
+      q.y = h22u(__floats2half2_rn(o0.y * g, o2.y * g));
+      q.z = h22u(__floats2half2_rn(o1.x * f, o3.x * f));
+      q.w = h22u(__floats2half2_rn(o1.y * g, o3.y * g));
+      *reinterpret_cast<uint4 *>(xs + threadIdx.x * 8) = q;
+      if ((threadIdx.x & 3) == 0) corr[threadIdx.x >> 2] = sx * (8.0f * 5.9604644775390625e-8f);
+    }
+  } else {
   unsigned mx[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) mx[m] = 0u;
@@ -169,7 +247,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 gf = __half22float2(u2h2(ga[j])), uf = __half22float2(u2h2(ua[j]));
-        o[j] = h22u(__floats2half2_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y));
+        o[j] = h22u(__floats2half2_rn(__fdividef(gf.x, 1.0f + __expf(-gf.x)) * uf.x, __fdividef(gf.y, 1.0f + __expf(-gf.y)) * uf.y));
       }
       const uint4 v = make_uint4(o[0], o[1], o[2], o[3]);
       track(v, m);
@@ -259,6 +337,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
       if (valid && (r & 3) == 0) corr[m * n_units + (r >> 2)] = sx * (8.0f * 5.9604644775390625e-8f);
     }
   }
+  }  // general prologue
   __syncthreads();
 
   float facc[M][4];
