@@ -144,12 +144,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   cg::cluster_group cluster = cg::this_cluster();
   const int splits = (int)cluster.num_blocks(), split = (int)cluster.block_rank();
   const int h = blockIdx.x / splits;
-  float *sc = att_smem;                      // [rows_per_cta] scores, then exp weights
-  float *red = sc + p.rows_per_cta;          // [16][128] partial P.V
+  float *red = att_smem;                     // [16][128] weighted V per half-warp
   float *inbox = red + 16 * ATT_D;           // [splits][128/splits] weighted V, then [splits] max, [splits] sum
   __shared__ __align__(16) __half q_s[ATT_D], k_s[ATT_D], v_s[ATT_D];
-  __shared__ float sh[32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ float hw_m[16], hw_l[16];
   const int chunk = threadIdx.x & 15, sgroup = threadIdx.x >> 4;  // 16-byte chunk of a row; row group (16 rows per pass)
 
   pdl_launch_dependents();
@@ -175,15 +173,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
       vreg[j] = ldg_stream_v4(vh + (size_t)s * p.kv_stride);
     }
   }
-  float freq = 0.f;
-  if (threadIdx.x < ATT_D / 2) freq = p.inv_freq[threadIdx.x];
+  float sn = 0.f, cs = 1.f;
+  if (threadIdx.x < ATT_D / 2) sincosf((float)pos * p.inv_freq[threadIdx.x], &sn, &cs);
   pdl_wait();
 
   // rotate q and k of this head (rotate-half), keep v
   if (threadIdx.x < ATT_D / 2) {
     const int j = threadIdx.x;
-    float sn, cs;
-    sincosf((float)pos * freq, &sn, &cs);
     const __half *q = p.vqk + HD + (size_t)h * ATT_D, *k = p.vqk + 2 * HD + (size_t)h * ATT_D;
     const float qa = __half2float(q[j]), qb = __half2float(q[j + ATT_D / 2]);
     const float ka = __half2float(k[j]), kb = __half2float(k[j + ATT_D / 2]);
@@ -202,98 +198,86 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     reinterpret_cast<uint4 *>(p.vc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(v_s)[threadIdx.x];
   }
 
-  // scores of this CTA's rows: 16 lanes per row, row i = sgroup + 16 * pass
+  // Each half-warp (16 lanes x 8 dims) runs an online softmax over its rows i = sgroup + 16 * pass:
+  // running max, running sum and the running weighted V, so scores never go through shared memory.
   float qf[8];
   h8_to_f8(reinterpret_cast<const uint4 *>(q_s)[chunk], qf);
-  float mx = -CUDART_INF_F;
-  auto score_row = [&](int i, uint4 kv) {
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  auto row_step = [&](bool live, uint4 kv, uint4 vv) {  // called by whole warps; `live` is per half-warp
     float dot = 0.f;
-    if (i < n_local) {
-      float kf[8];
-      h8_to_f8(kv, kf);
+    float kf[8];
+    h8_to_f8(kv, kf);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
-    }
+    for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (i < n_local) {
+    if (live) {
       dot *= p.scale;
-      if (chunk == 0) sc[i] = dot;
-      mx = fmaxf(mx, dot);
+      const float m_new = fmaxf(m_run, dot);
+      const float c = __expf(m_run - m_new), w = __expf(dot - m_new);  // first row: c = exp(-inf) = 0
+      float vf[8];
+      h8_to_f8(vv, vf);
+      l_run = fmaf(l_run, c, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(acc[j], c, w * vf[j]);
+      m_run = m_new;
     }
   };
 #pragma unroll
   for (int j = 0; j < ATT_PF; ++j) {
-    const int i = sgroup + 16 * j;
     if (16 * j < n_local) {  // uniform over the CTA
+      const int i = sgroup + 16 * j;
       const int s = split + i * splits;
-      score_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[chunk] : kreg[j]);
+      const bool cur = (s == pos);
+      row_step(i < n_local, cur ? reinterpret_cast<const uint4 *>(k_s)[chunk] : kreg[j], cur ? reinterpret_cast<const uint4 *>(v_s)[chunk] : vreg[j]);
     }
   }
   for (int i0 = 16 * ATT_PF; i0 < n_local; i0 += 16) {
     const int i = i0 + sgroup;
     const int s = split + i * splits;
-    uint4 kv = make_uint4(0, 0, 0, 0);
-    if (i < n_local) kv = (s == pos) ? reinterpret_cast<const uint4 *>(k_s)[chunk] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
-    score_row(i, kv);
-  }
-  mx = warp_max(mx);
-  if (lane == 0) sh[warp] = mx;
-  __syncthreads();
-  mx = (lane < ATT_THREADS / 32) ? sh[lane] : -CUDART_INF_F;
-  mx = warp_max(mx);
-  __syncthreads();
-  float sum = 0.f;
-  for (int i = threadIdx.x; i < n_local; i += ATT_THREADS) {
-    const float e = __expf(sc[i] - mx);
-    sc[i] = e;
-    sum += e;
-  }
-  sum = warp_sum(sum);
-  if (lane == 0) sh[warp] = sum;
-  __syncthreads();
-  sum = (lane < ATT_THREADS / 32) ? sh[lane] : 0.f;
-  sum = warp_sum(sum);
-
-  // partial P.V with the same thread -> (row, chunk) mapping
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  auto pv_row = [&](int i, uint4 vv) {
-    float vf[8];
-    h8_to_f8(vv, vf);
-    const float ps = sc[i];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps, vf[j], acc[j]);
-  };
-#pragma unroll
-  for (int j = 0; j < ATT_PF; ++j) {
-    const int i = sgroup + 16 * j;
-    if (i < n_local) {
-      const int s = split + i * splits;
-      pv_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[chunk] : vreg[j]);
+    const bool live = i < n_local, cur = (s == pos);
+    uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+    if (live) {
+      kv = cur ? reinterpret_cast<const uint4 *>(k_s)[chunk] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
+      vv = cur ? reinterpret_cast<const uint4 *>(v_s)[chunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride);
     }
-  }
-  for (int i = 16 * ATT_PF + sgroup; i < n_local; i += 16) {
-    const int s = split + i * splits;
-    pv_row(i, (s == pos) ? reinterpret_cast<const uint4 *>(v_s)[chunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride));
+    row_step(live, kv, vv);
   }
 #pragma unroll
   for (int j = 0; j < 8; ++j) red[sgroup * ATT_D + chunk * 8 + j] = acc[j];
+  if (chunk == 0) {
+    hw_m[sgroup] = m_run;
+    hw_l[sgroup] = l_run;
+  }
   __syncthreads();
-  // merge across the head's CTAs, push model: CTA r stores its un-normalised output slice, max and
-  // sum into the inbox of the CTA that finalises those dims; one cluster barrier; local merge.
+  // merge the 16 half-warp partials per dim, then across the head's CTAs, push model: CTA r stores its
+  // un-normalised output slice, max and sum into the inbox of the CTA that finalises those dims; one
+  // cluster barrier; local merge.
   const int dims_per = ATT_D / splits;
-  if (threadIdx.x < ATT_D) {
-    float t = 0.f;
+  if (threadIdx.x < ATT_D + splits) {
+    float mx = -CUDART_INF_F;
 #pragma unroll
-    for (int gI = 0; gI < 16; ++gI) t += red[gI * ATT_D + threadIdx.x];
-    const int owner = threadIdx.x / dims_per, dd = threadIdx.x - owner * dims_per;
-    float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
-    dst[split * dims_per + dd] = t;
-  } else if (threadIdx.x < ATT_D + splits) {
-    const int owner = threadIdx.x - ATT_D;
-    float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
-    dst[ATT_D + split] = mx;
-    dst[ATT_D + splits + split] = sum;
+    for (int gI = 0; gI < 16; ++gI) mx = fmaxf(mx, hw_m[gI]);
+    float l = 0.f, t = 0.f;
+    const int d = threadIdx.x < ATT_D ? threadIdx.x : 0;
+#pragma unroll
+    for (int gI = 0; gI < 16; ++gI) {
+      const float mg = hw_m[gI];
+      const float w = (mg == -CUDART_INF_F) ? 0.f : __expf(mg - mx);  // a half-warp without rows weighs nothing
+      l = fmaf(hw_l[gI], w, l);
+      t = fmaf(red[gI * ATT_D + d], w, t);
+    }
+    if (threadIdx.x < ATT_D) {
+      const int owner = threadIdx.x / dims_per, dd = threadIdx.x - owner * dims_per;
+      float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
+      dst[split * dims_per + dd] = t;
+    } else {
+      const int owner = threadIdx.x - ATT_D;
+      float *dst = (splits > 1) ? cluster.map_shared_rank(inbox, owner) : inbox;
+      dst[ATT_D + split] = mx;
+      dst[ATT_D + splits + split] = l;
+    }
   }
   if (splits > 1) cluster.sync(); else __syncthreads();
   if (threadIdx.x < dims_per) {
@@ -302,7 +286,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     for (int r = 0; r < splits; ++r) gm = fmaxf(gm, inbox[ATT_D + r]);
     float l = 0.f, o = 0.f;
     for (int r = 0; r < splits; ++r) {
-      const float w = __expf(inbox[ATT_D + r] - gm);  // a CTA without rows has max -inf -> weight 0
+      const float mr = inbox[ATT_D + r];
+      const float w = (mr == -CUDART_INF_F) ? 0.f : __expf(mr - gm);  // a CTA without rows weighs nothing
       l += inbox[ATT_D + splits + r] * w;
       o += inbox[r * dims_per + threadIdx.x] * w;
     }
@@ -405,7 +390,7 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   while (splits < 8 && H * splits * 2 <= 2 * sm_count()) splits *= 2;  // up to ~2 CTAs per SM, at most 8 per head
   AttnFusedParams p{(const __half *)vqk_f16, inv_freq, pos_dev, (__half *)k_cache_f16, (__half *)v_cache_f16, (__half *)out_f16,
                     H, max_seq, kv_stride, scale, (max_seq + splits - 1) / splits};
-  const size_t smem = ((size_t)p.rows_per_cta + 16 * ATT_D + ATT_D + 2 * 8) * sizeof(float);
+  const size_t smem = ((size_t)16 * ATT_D + ATT_D + 2 * 8) * sizeof(float);
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_fused: max_seq=%d exceeds the shared-memory score buffer", max_seq);
   if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};
