@@ -588,9 +588,10 @@ static int gemv_f16_scalar(GemvParams p, int M, int epi, cudaStream_t s) {
   return gemv_f16_direct<EPI_STORE_F32, PRO>(p, M, s);
 }
 
-// fp16 path.  Auto choice (measured on B200): batches of 1-2 rows on the scalar-pipe cluster kernel
-// (lowest fixed cost and best streaming rate at that size), 3-16 rows on the cluster warp-MMA
-// kernel (constant cost in the batch size).  The persistent warp-MMA kernel (option gemv_impl=3)
+// fp16 path.  Auto choice (measured on B200): one row on the scalar-pipe cluster kernel (lowest
+// fixed cost and best streaming rate at that size); 2-16 rows on the TMA-ring warp-MMA kernel
+// (cost nearly constant in the batch size) when the shape fits it (group 128, N % 8 == 0), else
+// 3-16 rows on the cluster warp-MMA kernel, else the scalar-pipe kernel.  The persistent warp-MMA kernel (option gemv_impl=3)
 // needs scratch; scratch == nullptr means the library-owned buffer.
 // One-shot prefetch hint of the calling thread (ab200_w4a16_gemv_prefetch_hint): consumed by the
 // next fp16 GEMV call, whichever kernel it picks (only the scalar-pipe kernel acts on it).
@@ -617,7 +618,7 @@ static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps
     }
     return gemv_persist_dispatch(x, norm_w, eps, qw, scales, out, M, K, N, group, pro, epi, scratch, s);
   }
-  if (impl == 4) {
+  if (impl == 4 || (impl == 0 && M >= 2)) {
     bool handled = false;
     const int rc = gemv_tma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
     if (rc || handled) return rc;

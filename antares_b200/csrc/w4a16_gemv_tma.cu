@@ -400,17 +400,22 @@ static bool tma_plan(int M, int MB, int stages, int tiles, TmaPlan &pl) {
     const int xs_stride = st_max * T_STAGE_K + T_XS_PAD;
     const size_t misc = 1024 + 256 + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15) + (size_t)3 * M * TILE_N * sizeof(float) +
                         (size_t)2 * st_max * MB * sizeof(float);
-    const int per_sm = (tiles * cs + sms - 1) / sms;
-    const size_t budget = (size_t)227 * 1024 / (per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm)) - 1024;  // 1 KiB per CTA is reserved by the system
-    int depth = (budget > misc) ? (int)((budget - misc) / (T_W_BYTES + T_S_BYTES)) : 0;
-    if (depth > st_max) depth = st_max;
-    if (depth > T_MAX_DEPTH) depth = T_MAX_DEPTH;
-    if (depth >= 2 || (depth >= 1 && st_max == 1)) {
-      pl.cs = cs;
-      pl.depth = depth;
-      pl.xs_stride = xs_stride;
-      pl.smem = misc + (size_t)depth * (T_W_BYTES + T_S_BYTES);
-      return true;
+    int per_sm = (tiles * cs + sms - 1) / sms;
+    if (per_sm > 3) per_sm = 3;
+    // prefer every CTA resident at once; with many batch rows the activations crowd the ring out,
+    // then fewer CTAs per SM with a deeper ring each
+    for (; per_sm >= 1; --per_sm) {
+      const size_t budget = (size_t)227 * 1024 / per_sm - 1024;  // 1 KiB per CTA is reserved by the system
+      int depth = (budget > misc) ? (int)((budget - misc) / (T_W_BYTES + T_S_BYTES)) : 0;
+      if (depth > st_max) depth = st_max;
+      if (depth > T_MAX_DEPTH) depth = T_MAX_DEPTH;
+      if (depth >= 2 || (depth >= 1 && st_max == 1)) {
+        pl.cs = cs;
+        pl.depth = depth;
+        pl.xs_stride = xs_stride;
+        pl.smem = misc + (size_t)depth * (T_W_BYTES + T_S_BYTES);
+        return true;
+      }
     }
     if (cs >= 8 || stages / (cs * 2) < 1) return false;
   }
