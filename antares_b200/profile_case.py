@@ -2,6 +2,7 @@
 decode steps of a shortened model.  Holds at most a few hundred MB on the device.
 
   python -m antares_b200.profile_case gemv K N M [--impl I] [--launches L]
+  python -m antares_b200.profile_case gemm M K N [--launches L]
   python -m antares_b200.profile_case step [--layers L] [--pos P] [--steps S]
 """
 import argparse
@@ -15,7 +16,7 @@ from .llama import LlamaConfig, LlamaInt4Decoder, synth_prompt
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "step"])
+    ap.add_argument("what", choices=["gemv", "gemm", "step"])
     ap.add_argument("dims", nargs="*", type=int)
     ap.add_argument("--impl", type=int, default=0)
     ap.add_argument("--launches", type=int, default=6)
@@ -35,6 +36,15 @@ def main():
         ops.set_option("gemv_impl", a.impl)
         for i in range(a.launches):
             ops.w4a16_gemv(x, qws[i % nbuf], scs[i % nbuf], out)
+        torch.cuda.synchronize()
+    elif a.what == "gemm":
+        M, K, N = a.dims
+        qw_np, sc_np = packing.synth_w4(K, N, 1)
+        qw, sc = torch.from_numpy(qw_np).to(dev), torch.from_numpy(sc_np).to(dev)
+        x = torch.from_numpy(packing.synth_x(M, K, 2)).to(dev)
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+        for i in range(a.launches):
+            ops.w4a16_gemm(x, qw, sc, out)
         torch.cuda.synchronize()
     else:
         cfg = LlamaConfig(n_layers=a.layers, max_seq=512)
