@@ -5,27 +5,39 @@
 // M axis larger than the decode path handles.  The dequantised weight fed to the tensor cores is
 // exactly w = RN_fp16(scale * fp16(q - 8)) (IR statement 2), the products accumulate in fp32.
 //
-// CTA tile 128 (M) x 256 (N), K step 64, two shared-memory stages.  All 256 threads fill a stage:
+// CTA tile 256 (M) x 256 (N), K step 64, three shared-memory stages, 512 threads, one CTA per SM.
+// The two 128-row halves of the tile have their own fp32 accumulator (2 x 256 TMEM columns) and
+// share every dequantised weight tile, which halves the dequantisation work per flop against a
+// 128-row tile.  All 512 threads fill a stage:
 //   A: x tile, 16-byte chunks copied into the K-major "core matrix" layout (8 rows x 16 B
-//      contiguous), each chunk's 8 k-values permuted to (k0,k4,k1,k5,k2,k6,k3,k7);
-//   B: thread t owns column n0 + t: each packed int32 word (8 consecutive k of one column) becomes
-//      one 16-byte row of a core matrix in the same k order (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the
-//      zero-point, HMUL2 by the group scale), so no transpose is needed and a quarter-warp writes
-//      128 contiguous bytes.
+//      contiguous), each chunk's 8 k-values permuted to (k0,k4,k1,k5,k2,k6,k3,k7); eight lanes read
+//      one row's whole 128-byte line, and the k chunks sit 2048 + 16 bytes apart (the descriptor's
+//      leading-dimension offset), which rotates the banks so that those stores do not conflict;
+//   B: thread t owns column n0 + t % 256 and four of the stage's eight packed rows: each packed
+//      int32 word (8 consecutive k of one column) becomes one 16-byte row of a core matrix in the
+//      same k order (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the zero-point, HMUL2 by the group
+//      scale), so no transpose is needed and a quarter-warp writes 128 contiguous bytes.
 // Since both operands carry the same permutation of k inside every group of 8, the contraction
-// is unchanged.  One thread then issues four `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
-// both operands K-major, no swizzle) per stage and commits them to an mbarrier; filling stage
-// s+1 overlaps the MMAs of stage s.  The 128x256 fp32 accumulator lives in 256 TMEM columns;
-// the epilogue reads it with `tcgen05.ld` (row = TMEM lane = thread), rounds to fp16 and stores.
+// is unchanged.  One thread then issues eight `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
+// both operands K-major, no swizzle; four K steps x two accumulators) per stage and commits them
+// to the stage's mbarrier; a stage is refilled once the MMAs that read it three iterations ago
+// have completed, so filling overlaps the MMAs of the two stages before.  The epilogue reads the
+// accumulators with `tcgen05.ld` (row = TMEM lane; the four warps that share a lane quarter split
+// the 512 columns), rounds to fp16 and stores.
 // Every mbarrier wait is bounded and reports through the status word.
 #include "common.cuh"
 
 namespace ab200 {
 
-constexpr int GM_BM = 128, GM_BN = 256, GM_BK = 64;
-constexpr int GM_THREADS = 256;
-constexpr int GM_STAGES = 2;
-constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;  // 16 KiB
+constexpr int GM_BM = 256, GM_BN = 256, GM_BK = 64;
+constexpr int GM_HM = 128;                     // rows per accumulator (one MMA's M)
+constexpr int GM_THREADS = 512;
+constexpr int GM_STAGES = 3;
+constexpr int GM_A_LBO = (GM_HM / 8) * 128 + 16;  // bytes between the k chunks of the x tile: 16 B of padding per chunk
+                                                   // rotates the banks, so that eight lanes holding one row's eight
+                                                   // chunks (a whole 128-B line of x) store without conflicts
+constexpr int GM_AH_BYTES = (GM_BK / 8) * GM_A_LBO;  // 16.1 KiB: one 128-row half of the x tile
+constexpr int GM_A_BYTES = 2 * GM_AH_BYTES;    // 32 KiB
 constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;  // 32 KiB
 constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
 constexpr unsigned GM_WAIT_POLLS = 1u << 22;
@@ -81,8 +93,8 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fail_s = 0;
   }
-  if (warp == 0) {  // one warp allocates the accumulator's 256 TMEM columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(&tmem_base_s)), "r"(GM_BN) : "memory");
+  if (warp == 0) {  // one warp allocates both accumulators: all 512 TMEM columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(&tmem_base_s)), "r"(2 * GM_BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -91,49 +103,63 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
   const uint32_t tmem_acc = tmem_base_s;
 
   // instruction descriptor: D fp32, A/B fp16, both K-major, N = 256, M = 128
-  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+  constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_HM >> 4) << 24);
 
   // ---- per-thread fill roles ---------------------------------------------------------------------------
-  // B: column n0 + tid (clamped), eight packed rows per stage
-  int nb = n0 + tid;
+  // B: column n0 + tid % 256 (clamped), packed rows bh*4 .. bh*4+3 of the stage's eight
+  const int bcol = tid & (GM_BN - 1), bh = tid >> 8;
+  int nb = n0 + bcol;
   const bool nb_ok = nb < N;
   if (!nb_ok) nb = N - 1;
-  const int32_t *bq = p.qw + nb;                      // + row * N
-  const __half *bs = p.scales + nb;                   // + (k / group) * N
-  const uint32_t b_off = (uint32_t)((tid >> 3) * 128 + (tid & 7) * 16);  // core matrix row of this column; + kc * 4096
-  // A: four 16-byte chunks per stage: row group mg, k chunk kc, row r8
-  const int r8 = lane & 7, kq = lane >> 3;
+  const int32_t *bq = p.qw + nb + (size_t)(bh * 4) * N;  // + row * N
+  const __half *bs = p.scales + nb;                      // + (k / group) * N
+  const uint32_t b_off = (uint32_t)((bcol >> 3) * 128 + (bcol & 7) * 16 + bh * 4 * (GM_BN / 8) * 128);  // + j * 4096
+  // A: four 16-byte chunks per stage.  Eight lanes read the 128 contiguous bytes of one row (whole
+  // L2 lines per request); a warp covers rows warp*16 + i*4 + lane/8.
   const __half *ax[4];
   uint32_t a_off[4];
   bool a_ok[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int mg = warp * 2 + (i >> 1), kc = (i & 1) * 4 + kq;
-    const int row = m0 + mg * 8 + r8;
+    const int rl = warp * 16 + i * 4 + (lane >> 3), kc = lane & 7;  // row within the 256-row tile, k chunk
+    const int mg = rl >> 3, r8 = rl & 7;
+    const int row = m0 + rl;
     a_ok[i] = row < M;
     ax[i] = p.x + (size_t)(a_ok[i] ? row : 0) * K + kc * 8;
-    a_off[i] = (uint32_t)((kc * 16 + mg) * 128 + r8 * 16);
+    a_off[i] = (uint32_t)((mg >> 4) * GM_AH_BYTES + kc * GM_A_LBO + (mg & 15) * 128 + r8 * 16);
   }
 
-  uint32_t breg[8];
-  uint4 areg[4];
-  __half sreg;
-  auto load_regs = [&](int kt) {  // global -> registers for k tile kt
+  // Three register sets: the global loads of k tile kt+3 are issued while tile kt is being written
+  // to shared memory.  The x tile is re-read from L2 by every column tile (43 times for N = 11008),
+  // which makes L2 -> SM traffic, not HBM, the limit of the fill; whole-line requests and deep
+  // prefetch are what it responds to.
+  struct FillRegs {
+    uint32_t b[4];
+    uint4 a[4];
+    __half s;
+  };
+  auto load_regs = [&](int kt, FillRegs &r) {  // global -> registers for k tile kt
     const int row0 = kt * (GM_BK / 8);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) breg[j] = (uint32_t)__ldg(bq + (size_t)(row0 + j) * N);
-    sreg = __ldg(bs + (size_t)((kt * GM_BK) / p.group) * N);
+    // volatile asm: the loads must be ISSUED here, three tiles ahead of their use, not sunk to it
+    for (int j = 0; j < 4; ++j) asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[j]) : "l"(bq + (size_t)(row0 + j) * N));
+    unsigned short sbits;
+    asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(sbits) : "l"(bs + (size_t)((kt * GM_BK) / p.group) * N));
+    r.s = __ushort_as_half(sbits);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) areg[i] = a_ok[i] ? __ldg(reinterpret_cast<const uint4 *>(ax[i] + (size_t)kt * GM_BK)) : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < 4; ++i) {
+      const __half *src = ax[i] + (size_t)kt * GM_BK;
+      asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r.a[i].x), "=r"(r.a[i].y), "=r"(r.a[i].z), "=r"(r.a[i].w) : "l"(src));
+      if (!a_ok[i]) r.a[i] = make_uint4(0, 0, 0, 0);
+    }
   };
 
   const int ktiles = K / GM_BK;
-  load_regs(0);
   bool ok = true;
-  for (int kt = 0; kt < ktiles; ++kt) {
+  auto k_step = [&](int kt, FillRegs &r) {
     const int s = kt % GM_STAGES;
     unsigned char *sa = gm_smem + s * GM_STAGE_BYTES, *sb = sa + GM_A_BYTES;
-    if (kt >= GM_STAGES) {  // the MMAs that read this stage two iterations ago must have finished
+    if (kt >= GM_STAGES) {  // the MMAs that read this stage GM_STAGES iterations ago must have finished
       if (!gm_mbar_wait(&mma_bar[s], ((kt / GM_STAGES) - 1) & 1)) {
         ok = false;
         fail_s = 1;
@@ -143,10 +169,10 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
     {
       constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
       const __half2 c1032 = u2h2(0x64086408u), c16th = u2h2(0x2C002C00u), cm72 = u2h2(0xD480D480u);
-      const __half2 sc2 = __half2half2(sreg);
+      const __half2 sc2 = __half2half2(r.s);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t w = breg[j], w8 = w >> 8;
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = r.b[j], w8 = w >> 8;
         uint4 o;  // (k0,k4)(k1,k5)(k2,k6)(k3,k7), each RN_fp16(scale * (q - 8))
         o.x = h22u(__hmul2(__hsub2(u2h2(lop3<0xEA>(w, LO, MAGIC)), c1032), sc2));
         o.y = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w, HI, MAGIC)), c16th, cm72), sc2));
@@ -157,7 +183,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint4 v = areg[i];
+        const uint4 v = r.a[i];
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
@@ -166,7 +192,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
         *reinterpret_cast<uint4 *>(sa + a_off[i]) = o;
       }
     }
-    if (kt + 1 < ktiles) load_regs(kt + 1);  // next tile's global loads fly during the MMAs
+    if (kt + 3 < ktiles) load_regs(kt + 3, r);  // this set's next tile: three MMA periods to arrive
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -175,18 +201,30 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
       const uint32_t a_base = gm_smem_u32(sa), b_base = gm_smem_u32(sb);
 #pragma unroll
       for (int kb = 0; kb < GM_BK / 16; ++kb) {
-        const uint64_t da = gm_desc(a_base + kb * 2 * (GM_BM / 8) * 128, (GM_BM / 8) * 128, 128);
         const uint64_t db = gm_desc(b_base + kb * 2 * (GM_BN / 8) * 128, (GM_BN / 8) * 128, 128);
         const uint32_t accumulate = (kt > 0 || kb > 0) ? 1u : 0u;
-        asm volatile(
-            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc),
-            "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
-            : "memory");
+#pragma unroll
+        for (int hm = 0; hm < 2; ++hm) {
+          const uint64_t da = gm_desc(a_base + hm * GM_AH_BYTES + kb * 2 * GM_A_LBO, GM_A_LBO, 128);
+          asm volatile(
+              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+              " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc + hm * GM_BN),
+              "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
+              : "memory");
+        }
       }
       // arrives on the barrier when every MMA issued so far has completed
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
     }
+  };
+  FillRegs r0, r1, r2;
+  load_regs(0, r0);
+  if (ktiles > 1) load_regs(1, r1);
+  if (ktiles > 2) load_regs(2, r2);
+  for (int kt = 0; kt < ktiles; kt += 3) {
+    k_step(kt, r0);
+    if (kt + 1 < ktiles) k_step(kt + 1, r1);
+    if (kt + 2 < ktiles) k_step(kt + 2, r2);
   }
   // ---- drain: the last commit covers every MMA -----------------------------------------------------
   {
@@ -200,12 +238,16 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
   __syncthreads();
   if (fail_s && tid == 0) atomicExch(p.status, 200);
 
-  // ---- epilogue: TMEM -> registers -> fp16 -> global; warps 0-3, thread = accumulator row ------------
-  if (warp < 4 && !fail_s) {
-    const int row = m0 + warp * 32 + lane;
-    const uint32_t taddr = tmem_acc + ((uint32_t)(warp * 32) << 16);
+  // ---- epilogue: TMEM -> registers -> fp16 -> global.  A warp reads the TMEM lanes of its quarter
+  // (warp % 4); the four warps of a quarter take 128 of the 512 columns each: columns 0-255 are the
+  // accumulator of tile rows 0-127, columns 256-511 that of rows 128-255.
+  if (!fail_s) {
+    const int q = warp & 3, cg = warp >> 2;
+    const int hm = cg >> 1, c_begin = (cg & 1) * 128;
+    const int row = m0 + hm * GM_HM + q * 32 + lane;
+    const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(hm * GM_BN);
 #pragma unroll 1
-    for (int c = 0; c < GM_BN; c += 16) {
+    for (int c = c_begin; c < c_begin + 128; c += 16) {
       uint32_t r[16];
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -237,7 +279,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
   (void)ok;
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(GM_BN) : "memory");
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * GM_BN) : "memory");
 }
 
 }  // namespace ab200
