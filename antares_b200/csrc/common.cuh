@@ -34,6 +34,7 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
   } while (0)
 
 int sm_count();  // SMs of the current device (cached per device)
+void *tensor_map_encoder();  // cuTensorMapEncodeTiled through the runtime's driver entry point query, or nullptr
 int *kernel_error_ptr();  // device address of the status word that ab200_kernel_status reads (nullptr on failure)
 
 // Programmatic dependent launch: when enabled (option "pdl"), kernels are launched with

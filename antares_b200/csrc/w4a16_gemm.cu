@@ -9,37 +9,38 @@
 // The two 128-row halves of the tile have their own fp32 accumulator (2 x 256 TMEM columns) and
 // share every dequantised weight tile, which halves the dequantisation work per flop against a
 // 128-row tile.  All 512 threads fill a stage:
-//   A: x tile, 16-byte chunks copied into the K-major "core matrix" layout (8 rows x 16 B
-//      contiguous), each chunk's 8 k-values permuted to (k0,k4,k1,k5,k2,k6,k3,k7); eight lanes read
-//      one row's whole 128-byte line, and the k chunks sit 2048 + 16 bytes apart (the descriptor's
-//      leading-dimension offset), which rotates the banks so that those stores do not conflict;
+//   A: the x tile arrives by TMA (`cp.async.bulk.tensor.2d`, one box of 64 k x 128 rows per
+//      accumulator half, 128-byte swizzle, completion on the stage's mbarrier): whole 128-byte lines
+//      from L2, no thread instructions, and the K-major 128B-swizzled layout the MMA reads natively;
 //   B: thread t owns column n0 + t % 256 and four of the stage's eight packed rows: each packed
-//      int32 word (8 consecutive k of one column) becomes one 16-byte row of a core matrix in the
-//      same k order (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the zero-point, HMUL2 by the group
-//      scale), so no transpose is needed and a quarter-warp writes 128 contiguous bytes.
-// Since both operands carry the same permutation of k inside every group of 8, the contraction
-// is unchanged.  One thread then issues eight `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
+//      int32 word (8 consecutive k of one column) becomes one 16-byte row of a K-major no-swizzle
+//      core matrix (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the zero-point, HMUL2 by the group scale,
+//      PRMT back to natural k order), so no transpose is needed and a quarter-warp writes 128
+//      contiguous bytes.
+// One thread then issues eight `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
 // both operands K-major, no swizzle; four K steps x two accumulators) per stage and commits them
 // to the stage's mbarrier; a stage is refilled once the MMAs that read it three iterations ago
-// have completed, so filling overlaps the MMAs of the two stages before.  The epilogue reads the
+// have completed, so filling overlaps the MMAs of the two stages before.  The issuing thread
+// lives in a 17th warp; producers and issuer meet only through mbarriers (weights ready, x tile
+// landed, MMAs done), there is no block-wide barrier inside the K loop.  The epilogue reads the
 // accumulators with `tcgen05.ld` (row = TMEM lane; the four warps that share a lane quarter split
 // the 512 columns), rounds to fp16 and stores.
 // Every mbarrier wait is bounded and reports through the status word.
+#include <cuda.h>  // CUtensorMap and its enums (types only)
+
 #include "common.cuh"
 
 namespace ab200 {
 
 constexpr int GM_BM = 256, GM_BN = 256, GM_BK = 64;
 constexpr int GM_HM = 128;                     // rows per accumulator (one MMA's M)
-constexpr int GM_THREADS = 512;
-constexpr int GM_STAGES = 3;
-constexpr int GM_A_LBO = (GM_HM / 8) * 128 + 16;  // bytes between the k chunks of the x tile: 16 B of padding per chunk
-                                                   // rotates the banks, so that eight lanes holding one row's eight
-                                                   // chunks (a whole 128-B line of x) store without conflicts
-constexpr int GM_AH_BYTES = (GM_BK / 8) * GM_A_LBO;  // 16.1 KiB: one 128-row half of the x tile
+constexpr int GM_FILL_THREADS = 512;               // 16 warps dequantise weights
+constexpr int GM_THREADS = GM_FILL_THREADS + 32;   // + one warp whose lane 0 issues TMA copies and MMAs
+constexpr int GM_STAGES = 3;    // stages of dequantised weights
+constexpr int GM_ASTAGES = 4;   // stages of the x tile: one more, so that its TMA copy is issued two k tiles ahead
+constexpr int GM_AH_BYTES = GM_HM * GM_BK * 2;  // 16 KiB: one 128-row half of the x tile (128 rows x 128 B)
 constexpr int GM_A_BYTES = 2 * GM_AH_BYTES;    // 32 KiB
 constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;  // 32 KiB
-constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
 constexpr unsigned GM_WAIT_POLLS = 1u << 22;
 
 struct GemmParams {
@@ -64,6 +65,18 @@ __device__ __forceinline__ uint64_t gm_desc(uint32_t smem_addr, uint32_t lbo_byt
   return d;                // base offset 0, layout type 0 (no swizzle)
 }
 
+// K-major operand in the 128-byte-swizzled layout TMA writes (rows of 128 B, 8-row atoms of 1024 B):
+// stride between atoms 1024 B, leading-dimension field unused (1), layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t gm_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 __device__ __forceinline__ bool gm_mbar_wait(uint64_t *bar, unsigned parity) {
   const uint32_t addr = gm_smem_u32(bar);
   for (unsigned i = 0; i < GM_WAIT_POLLS; ++i) {
@@ -78,9 +91,10 @@ __device__ __forceinline__ bool gm_mbar_wait(uint64_t *bar, unsigned parity) {
   return false;
 }
 
-__global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmParams p) {
-  extern __shared__ __align__(1024) unsigned char gm_smem[];
-  __shared__ __align__(8) uint64_t mma_bar[GM_STAGES];
+__global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char gm_smem_raw[];
+  unsigned char *gm_smem = gm_smem_raw + ((1024u - (gm_smem_u32(gm_smem_raw) & 1023u)) & 1023u);  // swizzle atoms need 1024-B alignment
+  __shared__ __align__(8) uint64_t mma_bar[GM_STAGES], b_full_bar[GM_STAGES], full_bar[GM_ASTAGES], a_free_bar[GM_ASTAGES];
   __shared__ uint32_t tmem_base_s;
   __shared__ int fail_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -89,7 +103,14 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
 
   if (tid == 0) {
     for (int s = 0; s < GM_STAGES; ++s)
+    {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&mma_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&b_full_bar[s])), "r"(GM_FILL_THREADS / 32));
+    }
+    for (int s = 0; s < GM_ASTAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&full_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&a_free_bar[s])));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fail_s = 0;
   }
@@ -114,28 +135,23 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
   const int32_t *bq = p.qw + nb + (size_t)(bh * 4) * N;  // + row * N
   const __half *bs = p.scales + nb;                      // + (k / group) * N
   const uint32_t b_off = (uint32_t)((bcol >> 3) * 128 + (bcol & 7) * 16 + bh * 4 * (GM_BN / 8) * 128);  // + j * 4096
-  // A: four 16-byte chunks per stage.  Eight lanes read the 128 contiguous bytes of one row (whole
-  // L2 lines per request); a warp covers rows warp*16 + i*4 + lane/8.
-  const __half *ax[4];
-  uint32_t a_off[4];
-  bool a_ok[4];
+  // A: thread 0 asks the TMA unit for the two 64 k x 128 row boxes of k tile kt
+  auto issue_a = [&](int kt) {
+    const int s = kt % GM_ASTAGES;
+    const uint32_t bar = gm_smem_u32(&full_bar[s]);
+    const uint32_t dst = gm_smem_u32(gm_smem + s * GM_A_BYTES);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(GM_A_BYTES) : "memory");
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int rl = warp * 16 + i * 4 + (lane >> 3), kc = lane & 7;  // row within the 256-row tile, k chunk
-    const int mg = rl >> 3, r8 = rl & 7;
-    const int row = m0 + rl;
-    a_ok[i] = row < M;
-    ax[i] = p.x + (size_t)(a_ok[i] ? row : 0) * K + kc * 8;
-    a_off[i] = (uint32_t)((mg >> 4) * GM_AH_BYTES + kc * GM_A_LBO + (mg & 15) * 128 + r8 * 16);
-  }
+    for (int hm = 0; hm < 2; ++hm)
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst + hm * GM_AH_BYTES),
+                   "l"(reinterpret_cast<uint64_t>(&tm_x)), "r"(kt * GM_BK), "r"(m0 + hm * GM_HM), "r"(bar)
+                   : "memory");
+  };
 
-  // Three register sets: the global loads of k tile kt+3 are issued while tile kt is being written
-  // to shared memory.  The x tile is re-read from L2 by every column tile (43 times for N = 11008),
-  // which makes L2 -> SM traffic, not HBM, the limit of the fill; whole-line requests and deep
-  // prefetch are what it responds to.
+  // Three register sets for the packed weights: the global loads of k tile kt+3 are issued while
+  // tile kt is being written to shared memory.
   struct FillRegs {
     uint32_t b[4];
-    uint4 a[4];
     __half s;
   };
   auto load_regs = [&](int kt, FillRegs &r) {  // global -> registers for k tile kt
@@ -146,26 +162,23 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
     unsigned short sbits;
     asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(sbits) : "l"(bs + (size_t)((kt * GM_BK) / p.group) * N));
     r.s = __ushort_as_half(sbits);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __half *src = ax[i] + (size_t)kt * GM_BK;
-      asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r.a[i].x), "=r"(r.a[i].y), "=r"(r.a[i].z), "=r"(r.a[i].w) : "l"(src));
-      if (!a_ok[i]) r.a[i] = make_uint4(0, 0, 0, 0);
-    }
   };
 
   const int ktiles = K / GM_BK;
   bool ok = true;
-  auto k_step = [&](int kt, FillRegs &r) {
+  // Producer warps (0-15): per k tile wait until the MMAs that read the stage three tiles ago are
+  // done, write the dequantised weights, make them visible to the tensor core and arrive (one
+  // arrive per warp) on the stage's "weights ready" barrier.  No block-wide barrier in the loop:
+  // warps drift apart and hide each other's latencies.
+  auto fill_step = [&](int kt, FillRegs &r) {
     const int s = kt % GM_STAGES;
-    unsigned char *sa = gm_smem + s * GM_STAGE_BYTES, *sb = sa + GM_A_BYTES;
-    if (kt >= GM_STAGES) {  // the MMAs that read this stage GM_STAGES iterations ago must have finished
+    unsigned char *sb = gm_smem + GM_ASTAGES * GM_A_BYTES + s * GM_B_BYTES;
+    if (kt >= GM_STAGES) {
       if (!gm_mbar_wait(&mma_bar[s], ((kt / GM_STAGES) - 1) & 1)) {
         ok = false;
         fail_s = 1;
       }
     }
-    // ---- fill the stage from registers -------------------------------------------------------------
     {
       constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x64006400u;
       const __half2 c1032 = u2h2(0x64086408u), c16th = u2h2(0x2C002C00u), cm72 = u2h2(0xD480D480u);
@@ -179,52 +192,69 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
         o.z = h22u(__hmul2(__hsub2(u2h2(lop3<0xEA>(w8, LO, MAGIC)), c1032), sc2));
         o.w = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w8, HI, MAGIC)), c16th, cm72), sc2));
         if (!nb_ok) o = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(sb + j * (GM_BN / 8) * 128 + b_off) = o;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 v = r.a[i];
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410);
-        o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410);
-        o.w = __byte_perm(v.y, v.w, 0x7632);
-        *reinterpret_cast<uint4 *>(sa + a_off[i]) = o;
+        uint4 n;  // back to natural k order: (k0,k1)(k2,k3)(k4,k5)(k6,k7)
+        n.x = __byte_perm(o.x, o.y, 0x5410);
+        n.y = __byte_perm(o.z, o.w, 0x5410);
+        n.z = __byte_perm(o.x, o.y, 0x7632);
+        n.w = __byte_perm(o.z, o.w, 0x7632);
+        *reinterpret_cast<uint4 *>(sb + j * (GM_BN / 8) * 128 + b_off) = n;
       }
     }
     if (kt + 3 < ktiles) load_regs(kt + 3, r);  // this set's next tile: three MMA periods to arrive
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_base = gm_smem_u32(sa), b_base = gm_smem_u32(sb);
-#pragma unroll
-      for (int kb = 0; kb < GM_BK / 16; ++kb) {
-        const uint64_t db = gm_desc(b_base + kb * 2 * (GM_BN / 8) * 128, (GM_BN / 8) * 128, 128);
-        const uint32_t accumulate = (kt > 0 || kb > 0) ? 1u : 0u;
-#pragma unroll
-        for (int hm = 0; hm < 2; ++hm) {
-          const uint64_t da = gm_desc(a_base + hm * GM_AH_BYTES + kb * 2 * GM_A_LBO, GM_A_LBO, 128);
-          asm volatile(
-              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-              " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc + hm * GM_BN),
-              "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
-              : "memory");
-        }
-      }
-      // arrives on the barrier when every MMA issued so far has completed
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
-    }
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&b_full_bar[s])) : "memory");
   };
-  FillRegs r0, r1, r2;
-  load_regs(0, r0);
-  if (ktiles > 1) load_regs(1, r1);
-  if (ktiles > 2) load_regs(2, r2);
-  for (int kt = 0; kt < ktiles; kt += 3) {
-    k_step(kt, r0);
-    if (kt + 1 < ktiles) k_step(kt + 1, r1);
-    if (kt + 2 < ktiles) k_step(kt + 2, r2);
+  // Issuer (lane 0 of warp 16): keeps the x ring two k tiles ahead and issues the MMAs of a k tile
+  // as soon as its weights and its x tile are in shared memory.
+  auto issue_step = [&](int kt) {
+    const int s = kt % GM_STAGES, sA = kt % GM_ASTAGES;
+    if (kt + 2 < ktiles) {  // x tile two k tiles ahead: its stage was last read by the MMAs of kt - 2
+      const int s2 = (kt + 2) % GM_ASTAGES;
+      if (kt + 2 >= GM_ASTAGES && !gm_mbar_wait(&a_free_bar[s2], (((kt + 2) / GM_ASTAGES) - 1) & 1)) {
+        ok = false;
+        fail_s = 1;
+      }
+      issue_a(kt + 2);
+    }
+    if (!gm_mbar_wait(&b_full_bar[s], (kt / GM_STAGES) & 1) || !gm_mbar_wait(&full_bar[sA], (kt / GM_ASTAGES) & 1)) {
+      ok = false;
+      fail_s = 1;
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t a_base = gm_smem_u32(gm_smem + sA * GM_A_BYTES), b_base = gm_smem_u32(gm_smem + GM_ASTAGES * GM_A_BYTES + s * GM_B_BYTES);
+#pragma unroll
+    for (int kb = 0; kb < GM_BK / 16; ++kb) {
+      const uint64_t db = gm_desc(b_base + kb * 2 * (GM_BN / 8) * 128, (GM_BN / 8) * 128, 128);
+      const uint32_t accumulate = (kt > 0 || kb > 0) ? 1u : 0u;
+#pragma unroll
+      for (int hm = 0; hm < 2; ++hm) {
+        const uint64_t da = gm_desc_sw128(a_base + hm * GM_AH_BYTES + kb * 32);  // 16 k = 32 B further into the swizzled row
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc + hm * GM_BN),
+            "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
+            : "memory");
+      }
+    }
+    // arrive on the barriers when every MMA issued so far has completed
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&a_free_bar[sA])) : "memory");
+  };
+  if (warp < GM_FILL_THREADS / 32) {
+    FillRegs r0, r1, r2;
+    load_regs(0, r0);
+    if (ktiles > 1) load_regs(1, r1);
+    if (ktiles > 2) load_regs(2, r2);
+    for (int kt = 0; kt < ktiles; kt += 3) {
+      fill_step(kt, r0);
+      if (kt + 1 < ktiles) fill_step(kt + 1, r1);
+      if (kt + 2 < ktiles) fill_step(kt + 2, r2);
+    }
+  } else if (lane == 0) {
+    issue_a(0);
+    if (ktiles > 1) issue_a(1);
+    for (int kt = 0; kt < ktiles; ++kt) issue_step(kt);
   }
   // ---- drain: the last commit covers every MMA -----------------------------------------------------
   {
@@ -241,7 +271,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(GemmPara
   // ---- epilogue: TMEM -> registers -> fp16 -> global.  A warp reads the TMEM lanes of its quarter
   // (warp % 4); the four warps of a quarter take 128 of the 512 columns each: columns 0-255 are the
   // accumulator of tile rows 0-127, columns 256-511 that of rows 128-255.
-  if (!fail_s) {
+  if (!fail_s && warp < GM_FILL_THREADS / 32) {
     const int q = warp & 3, cg = warp >> 2;
     const int hm = cg >> 1, c_begin = (cg & 1) * 128;
     const int row = m0 + hm * GM_HM + q * 32 + lane;
@@ -298,10 +328,24 @@ extern "C" int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const voi
   int *status = kernel_error_ptr();
   AB200_REQUIRE(status != nullptr, "w4a16_gemm: cannot resolve the status word");
   GemmParams p{(const __half *)x, qweight, (const __half *)scales, (__half *)out, M, K, N, group, status};
-  const size_t smem = (size_t)GM_STAGES * GM_STAGE_BYTES + 1024;
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+  EncodeFn enc = reinterpret_cast<EncodeFn>(tensor_map_encoder());
+  if (!enc) return fail(AB200_EUNSUPPORTED, "w4a16_gemm: this driver has no cuTensorMapEncodeTiled");
+  CUtensorMap tm_x;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {GM_BK, GM_HM}, estr[2] = {1, 1};
+    const CUresult r = enc(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AB200_ECUDA, "w4a16_gemm: cuTensorMapEncodeTiled(x) failed with %d", (int)r);
+  }
+  const size_t smem = (size_t)GM_ASTAGES * GM_A_BYTES + (size_t)GM_STAGES * GM_B_BYTES + 1024;
   AB200_CUDA(cudaFuncSetAttribute(w4a16_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const dim3 grid((N + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM);
-  w4a16_gemm_tcgen05_kernel<<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(p);
+  w4a16_gemm_tcgen05_kernel<<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(tm_x, p);
   AB200_CHECK_LAUNCH("w4a16_gemm");
   return AB200_OK;
 }

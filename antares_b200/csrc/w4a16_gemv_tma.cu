@@ -361,7 +361,10 @@ typedef CUresult (*TmaEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, 
                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static TmaEncodeFn tma_encoder() {
+void *tensor_map_encoder();
+static TmaEncodeFn tma_encoder() { return reinterpret_cast<TmaEncodeFn>(tensor_map_encoder()); }
+// cuTensorMapEncodeTiled, fetched through the runtime (no link against the driver library); nullptr if absent
+void *tensor_map_encoder() {
   static TmaEncodeFn fn = nullptr;
   static bool tried = false;
   if (!tried) {
@@ -372,7 +375,7 @@ static TmaEncodeFn tma_encoder() {
       fn = reinterpret_cast<TmaEncodeFn>(ptr);
     (void)cudaGetLastError();
   }
-  return fn;
+  return reinterpret_cast<void *>(fn);
 }
 
 static unsigned g_tma_wait_polls = 1u << 22;
