@@ -17,8 +17,9 @@
 // -8 * sum(x) * 2^-24 per group, fp32 sums are scaled by 2^24 at the end.  A consumer warp
 // releases a stage with one mbarrier arrive; the producer refills it as soon as all eight have.
 //
-// Split-K: the stages of a column tile are divided over the CTAs of a thread-block cluster, which
-// meet in distributed shared memory in fixed order (bitwise repeatable; no scratch, no atomics).
+// Split-K: the stages of a column tile are divided over the CTAs of a thread-block cluster; every
+// CTA pushes its column sums into the owner CTA's inbox in distributed shared memory, one cluster
+// barrier, rank-ordered sum (bitwise repeatable; no scratch, no atomics, no remote reads).
 // Every mbarrier wait is bounded: when one runs out the kernel stores a site code in the status
 // word (ab200_kernel_status), stops waiting and finishes with whatever it has.
 #include <cooperative_groups.h>
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
   const int k_begin = st_begin * T_STAGE_K;
   const int xs_stride = p.xs_stride;
 
-  // shared memory: [ring of weights, 1024-aligned][ring of scales][mbarriers][256 B zeros][x][red][part][seeds]
+  // shared memory: [ring of weights, 1024-aligned][ring of scales][mbarriers][256 B zeros][x][inbox][seeds]
   const uint32_t base_u32 = t_smem_u32(t_smem);
   const uint32_t ring_w = (base_u32 + 1023u) & ~1023u;
   unsigned char *ring_wp = t_smem + (ring_w - base_u32);
@@ -105,8 +106,8 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
   const uint32_t bars = ring_s + D * T_S_BYTES;  // full[D], empty[D]
   unsigned char *misc = ring_sp + D * T_S_BYTES + 256;  // 16 * D <= 128 bytes of barriers, rounded to 256
   __half *xs = reinterpret_cast<__half *>(misc + 256);
-  float *red = reinterpret_cast<float *>(misc + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));  // [2][M][128]
-  float *part = red + 2 * M * TILE_N;                                                                       // [M][128]
+  float *red = reinterpret_cast<float *>(ring_wp);  // [2][M][128]: reuses the ring once every consumer has left the K loop
+  float *part = reinterpret_cast<float *>(misc + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15));  // [M][128] inbox of the cluster reduction
   float *corr = part + M * TILE_N;  // [2 * stages of this slice][MB]
 
   if (threadIdx.x == 0) {
@@ -321,6 +322,7 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
       }
     }
 
+    asm volatile("bar.sync 1, %0;" ::"n"(T_CTHREADS) : "memory");  // every consumer is done with the ring: `red` may overwrite it
     // facc[nb][j][i]: column wn*32 + chunk*4 + 2j + (i>>1), batch nb*8 + 2t + (i&1)
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
@@ -334,25 +336,27 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
   }
   __syncthreads();
 
-  // ---- reduction: K halves -> CTA partial -> cluster (fixed order) -> epilogue --------------------
-  for (int i = threadIdx.x; i < M * TILE_N; i += T_THREADS) part[i] = red[i] + red[M * TILE_N + i];
-  if (cs > 1) cluster.sync(); else __syncthreads();
+  // ---- reduction: K halves -> owner CTA's inbox (push) -> one cluster barrier -> rank-ordered sum -> epilogue
   const int cols_per = TILE_N / cs;
+  for (int i = threadIdx.x; i < M * TILE_N; i += T_THREADS) {
+    const int m = i / TILE_N, c = i - m * TILE_N;
+    const float v = red[i] + red[M * TILE_N + i];
+    const int owner = c / cols_per, cc = c - owner * cols_per;
+    float *inbox = (cs > 1) ? cluster.map_shared_rank(part, owner) : part;
+    inbox[(krank * M + m) * cols_per + cc] = v;
+  }
+  if (cs > 1) cluster.sync(); else __syncthreads();
   for (int i = threadIdx.x; i < M * cols_per; i += T_THREADS) {
-    const int m = i / cols_per, c = krank * cols_per + i % cols_per;
+    const int m = i / cols_per, cc = i - m * cols_per;
     float s = 0.f;
-    for (unsigned r = 0; r < cs; ++r) {
-      const float *remote = (cs > 1) ? cluster.map_shared_rank(part, r) : part;
-      s += remote[m * TILE_N + c];
-    }
-    const int n = tile_n0 + c;
+    for (unsigned r = 0; r < cs; ++r) s += part[(r * M + m) * cols_per + cc];
+    const int n = tile_n0 + krank * cols_per + cc;
     if (n < N) {
       if (EPI == EPI_STORE) reinterpret_cast<__half *>(p.out)[(size_t)m * N + n] = __float2half_rn(s);
       else if (EPI == EPI_STORE_F32) reinterpret_cast<float *>(p.out)[(size_t)m * N + n] = s;
       else reinterpret_cast<float *>(p.out)[(size_t)m * N + n] += __half2float(__float2half_rn(s));
     }
   }
-  if (cs > 1) cluster.sync();
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -401,7 +405,7 @@ static bool tma_plan(int M, int MB, int stages, int tiles, TmaPlan &pl) {
   for (;; cs *= 2) {
     const int st_max = (stages + cs - 1) / cs;
     const int xs_stride = st_max * T_STAGE_K + T_XS_PAD;
-    const size_t misc = 1024 + 256 + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15) + (size_t)3 * M * TILE_N * sizeof(float) +
+    const size_t misc = 1024 + 256 + 256 + (((size_t)M * xs_stride * 2 + 15) & ~(size_t)15) + (size_t)M * TILE_N * sizeof(float) +
                         (size_t)2 * st_max * MB * sizeof(float);
     int per_sm = (tiles * cs + sms - 1) / sms;
     if (per_sm > 3) per_sm = 3;
