@@ -208,10 +208,15 @@ class LlamaInt4Decoder:
         call("ab200_rmsnorm", self.x.data_ptr(), 1, self.final_norm.data_ptr(), self.xb.data_ptr(), 1, cfg.dim, cfg.eps, st)
         call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), cfg.dim, self.vl, st)
         self._n += 2
-        if self.world > 1:
-            self.comm.all_gather_into(self.logits, self.logits_local)
-        call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), self._n_prompt_capture,
-             self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), st)
+        if self.world > 1 and hasattr(self.comm, "greedy_next_"):
+            # vocabulary-parallel argmax: candidates exchanged by peer stores, no gather of logits
+            self.comm.greedy_next_(self.logits_local, self.rank * self.vl, self.prompt, self._n_prompt_capture,
+                                   self.token, self.pos, self.out_tokens)
+        else:
+            if self.world > 1:
+                self.comm.all_gather_into(self.logits, self.logits_local)
+            call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), self._n_prompt_capture,
+                 self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), st)
         self._n += 1
         self.launches_per_step = self._n
 

@@ -59,34 +59,46 @@ class TorchComm:
 class PushComm(TorchComm):
     """TorchComm plus the one-shot push all-reduce over NVLink peer memory (csrc/comm.cu): every
     rank owns a receive buffer, maps its peers' buffers through CUDA IPC and the exchange is one
-    kernel per rank (peer stores, epoch flags, bounded wait, rank-ordered sum fused with the
+    kernel per rank (peer stores of (value, epoch) pairs, bounded wait, rank-ordered sum fused with the
     residual update).  torch.distributed is used only to swap the 64-byte IPC handles."""
 
     def __init__(self, device, n_max, group=None):
-        import ctypes
-        from ._lib import call
         super().__init__(group)
         self.device, self.n_max = device, int(n_max)
         torch.cuda.set_device(device)
+        self._own, self._peers, self._bufs = self._make_buffers(self.n_max)
+        # a second, tiny exchange buffer for the vocabulary-parallel greedy step
+        self._own_g, self._peers_g, self._bufs_g = self._make_buffers(4)
+        dist.barrier(group=group)
+
+    def _make_buffers(self, n_max):
+        import ctypes
+        from ._lib import call
         ptr = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        call("ab200_comm_alloc", self.world, self.n_max, ctypes.cast(ctypes.pointer(ptr), ctypes.c_void_p), ctypes.cast(handle, ctypes.c_void_p))
-        self._own = ptr.value
+        call("ab200_comm_alloc", self.world, n_max, ctypes.cast(ctypes.pointer(ptr), ctypes.c_void_p), ctypes.cast(handle, ctypes.c_void_p))
         handles = [None] * self.world
-        dist.all_gather_object(handles, handle.raw, group=group)
-        self._peers = []
+        dist.all_gather_object(handles, handle.raw, group=self.group)
+        peers = []
         bufs = (ctypes.c_void_p * self.world)()
         for r, h in enumerate(handles):
             if r == self.rank:
-                bufs[r] = self._own
+                bufs[r] = ptr.value
             else:
                 p = ctypes.c_void_p()
                 hb = ctypes.create_string_buffer(h, 64)
                 call("ab200_comm_open", ctypes.cast(hb, ctypes.c_void_p), ctypes.cast(ctypes.pointer(p), ctypes.c_void_p))
                 bufs[r] = p.value
-                self._peers.append(p.value)
-        self._bufs = bufs
-        dist.barrier(group=group)
+                peers.append(p.value)
+        return ptr.value, peers, bufs
+
+    def greedy_next_(self, logits_local, vocab_offset, prompt, n_prompt, token, pos, out_tokens):
+        """Vocabulary-parallel argmax + loop bookkeeping in one kernel per rank, no NCCL."""
+        import ctypes
+        from ._lib import call
+        call("ab200_greedy_next_tp", logits_local.data_ptr(), logits_local.numel(), int(vocab_offset),
+             ctypes.cast(self._bufs_g, ctypes.c_void_p), self.rank, self.world, 4, prompt.data_ptr(), int(n_prompt),
+             token.data_ptr(), pos.data_ptr(), out_tokens.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
     def all_reduce_residual_(self, x_f32, partial_f32):
         """x += fp16_round(sum over ranks of partial): one kernel, no NCCL."""
@@ -100,9 +112,10 @@ class PushComm(TorchComm):
         from ._lib import call
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
-        for p in self._peers:
+        for p in self._peers + self._peers_g:
             call("ab200_comm_close", p)
-        self._peers = []
-        if self._own:
-            call("ab200_comm_free", self._own)
-            self._own = None
+        self._peers, self._peers_g = [], []
+        for own in (self._own, self._own_g):
+            if own:
+                call("ab200_comm_free", own)
+        self._own = self._own_g = None

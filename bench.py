@@ -257,7 +257,7 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
 
 def extras_single_ops(torch, dev, peak_gbs, tensor_peak):
     """Operator-level figures next to the headline (rank 0, N=1): the W4A16 prefill GEMM of BASELINE
-    config 3 on the tensor cores and the four decode GEMV shapes of config 2 at batch 1, each timed
+    config 3 on the tensor cores and the four decode GEMV shapes of config 2 at batch 1, 8 and 16, each timed
     alone with CUDA events (GEMVs rotate through weight copies larger than L2)."""
     import numpy as np
     from antares_b200 import ops, packing
@@ -282,38 +282,40 @@ def extras_single_ops(torch, dev, peak_gbs, tensor_peak):
     out["prefill_gemm"] = {"shape": [M, K, N], "ms": ms, "tflops": tf, "peak_tflops": tensor_peak, "frac": tf / tensor_peak,
                            "kernel": "w4a16_gemm_tcgen05_kernel"}
     del qd, sd, x, y
-    gemv = {}
-    for name, (K, N) in (("o", (4096, 4096)), ("vqk", (4096, 12288)), ("gate_up", (4096, 22016)), ("down", (11008, 4096))):
-        qw, sc = packing.synth_w4(K, N, 3)
-        nbuf = int(300e6 // (qw.nbytes + sc.nbytes)) + 2
-        qs = [torch.from_numpy(qw).to(dev) for _ in range(nbuf)]
-        ss = [torch.from_numpy(sc).to(dev) for _ in range(nbuf)]
-        x = torch.from_numpy(packing.synth_x(1, K, 4)).to(dev)
-        y = torch.empty((1, N), dtype=torch.float16, device=dev)
-        side = torch.cuda.Stream(device=dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for i in range(3):
-                ops.w4a16_gemv(x, qs[i % nbuf], ss[i % nbuf], y)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                for i in range(2 * nbuf):
+    for M in (1, 8, 16):
+        gemv = {}
+        for name, (K, N) in (("o", (4096, 4096)), ("vqk", (4096, 12288)), ("gate_up", (4096, 22016)), ("down", (11008, 4096))):
+            qw, sc = packing.synth_w4(K, N, 3)
+            nbuf = int(300e6 // (qw.nbytes + sc.nbytes)) + 2
+            qs = [torch.from_numpy(qw).to(dev) for _ in range(nbuf)]
+            ss = [torch.from_numpy(sc).to(dev) for _ in range(nbuf)]
+            x = torch.from_numpy(packing.synth_x(M, K, 4)).to(dev)
+            y = torch.empty((M, N), dtype=torch.float16, device=dev)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(3):
                     ops.w4a16_gemv(x, qs[i % nbuf], ss[i % nbuf], y)
-            g.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            g.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (2 * nbuf)
-        torch.cuda.current_stream().wait_stream(side)
-        alg = K * N // 2 + (K // 128) * N * 2 + K * 2 + N * 2
-        gemv[name] = {"K": K, "N": N, "us": us, "GBs": alg / us / 1e3, "frac": alg / us / 1e3 / peak_gbs}
-        del qs, ss, g
-    out["gemv_m1"] = gemv
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(2 * nbuf):
+                        ops.w4a16_gemv(x, qs[i % nbuf], ss[i % nbuf], y)
+                g.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (2 * nbuf)
+            torch.cuda.current_stream().wait_stream(side)
+            alg = K * N // 2 + (K // 128) * N * 2 + M * K * 2 + M * N * 2
+            gemv[name] = {"K": K, "N": N, "us": us, "GBs": alg / us / 1e3, "frac": alg / us / 1e3 / peak_gbs}
+            del qs, ss, g
+        out["gemv_m%d" % M] = gemv
     return out
+
 
 
 def run_ours(args):
@@ -399,7 +401,8 @@ def run_ours(args):
             "step_hbm": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (sec / K) / 1e9,
                          "frac_of_peak": step_bytes / (sec / K) / 1e9 / peak},
             "tokens_match_between_runs": bool((tokens == tokens_e2e).all()),
-            "first_generated": [int(t) for t in tokens[N_PROMPT:N_PROMPT + 8]]}
+            "first_generated": [int(t) for t in tokens[N_PROMPT:N_PROMPT + 8]],
+            "tokens_crc32": int(__import__("zlib").crc32(tokens.astype("int32").tobytes()))}
     if world == 1 and not args.no_extras:
         tensor_peak = 1642.0
         path = os.path.join(ROOT, "MEASURED_PEAKS.json")

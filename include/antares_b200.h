@@ -253,6 +253,16 @@ int ab200_comm_free(void *buf);
 int ab200_allreduce_residual(float *x_f32, const float *partial_f32, int n, void *const *bufs_host,
                              int rank, int world, int n_max, void *stream);
 
+/* Vocabulary-parallel greedy step over the same kind of exchange buffer (its own one, n_max >= 4):
+ * argmax of this rank's logits shard, exchange of the per-rank (value, global index) candidates by
+ * peer stores, same winner on every rank (highest value, lowest index on ties), then the
+ * bookkeeping of ab200_greedy_next.  Replaces the logits all-gather of the reference's
+ * classifier step (samples/05_llama2_7b_int4.py:176-178) in tensor-parallel runs. */
+int ab200_greedy_next_tp(const float *logits_local_f32, int n_local, int vocab_offset,
+                         void *const *bufs_host, int rank, int world, int n_max,
+                         const int32_t *prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,
+                         int32_t *out_tokens, void *stream);
+
 /* The same protocol with all `world` ranks run as the blocks of ONE cooperative launch on one
  * GPU (x_host[r], partial_host[r], bufs_host[r] = rank r's device pointers): lets the exchange
  * be tested on fewer GPUs than ranks.  emu_scratch_dev: ab200_comm_emulation_scratch_bytes()
