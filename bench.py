@@ -52,17 +52,27 @@ def measured_peaks():
 
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi in loop mode beside the run.  It needs a few hundred ms to come up, so it is started
+    before the warm-up phase and only the samples stamped inside [mark_begin, mark_end] (host clock)
+    are used; if the timed region was shorter than the sampling period, the samples closest to it."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.proc = index, None
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -76,22 +86,33 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]), [n for n, v in zip(names, parts[4:8]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        t0 = self.t0 if self.t0 is not None else float("-inf")
+        t1 = self.t1 if self.t1 is not None else float("inf")
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        note = None
+        if not inside and rows:  # timed region shorter than the sampling period: take the two nearest samples
+            inside = sorted(rows, key=lambda r: min(abs(r[0] - t0), abs(r[0] - t1)))[:2]
+            note = "no sample fell inside the timed region; nearest samples used"
+        sm = [r[1] for r in inside]
+        mx = [r[2] for r in inside]
+        reasons = sorted({n for r in inside for n in r[3]})
+        res = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "samples": len(sm), "reasons": reasons}
+        if note:
+            res["note"] = note
+        return res
 
 
 # ---- reference arm: the reference's CPU runtime on the same operator chain -------------------------
@@ -354,16 +375,18 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-timed run ---------------------------------------------------------------------------
-    prefill_and_warm()
     sampler = ClockSampler(local_rank)
-    fence()
     sampler.start()
+    prefill_and_warm()
+    fence()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     e0.record()
     for _ in range(K):
         dec.graph.replay()
     e1.record()
     fence()
+    sampler.mark_end()
     clocks = sampler.stop()
     sec = e0.elapsed_time(e1) * 1e-3
     if comm is not None:
