@@ -110,9 +110,10 @@ class LlamaInt4Decoder:
 
     `comm` is None for world=1, otherwise an object with
       all_reduce_sum_(t_f32)  and  all_gather_into(out, t)   (see parallel.py).
+    `weights` selects the checkpoint (gptq.GptqLlamaWeights); None = seeded synthetic weights.
     """
 
-    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0):
+    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None):
         assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
         self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         self.hl = cfg.n_heads // world            # local heads
@@ -122,10 +123,12 @@ class LlamaInt4Decoder:
         self.vl = cfg.vocab // world
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
         self.layers = []
+        # `weights`: any object with layer(l) and globals() (e.g. gptq.GptqLlamaWeights); default: seeded synthetic weights
         for l in range(cfg.n_layers):
-            w = shard_layer(cfg, synth_layer(cfg, l), rank, world)
+            full = weights.layer(l) if weights is not None else synth_layer(cfg, l)
+            w = shard_layer(cfg, full, rank, world)
             self.layers.append({k: t(v) for k, v in w.items()})
-        gl = synth_globals(cfg)
+        gl = weights.globals() if weights is not None else synth_globals(cfg)
         self.embed = t(gl["embed"])
         self.lm_head = t(gl["lm_head"][rank * self.vl:(rank + 1) * self.vl])
         self.final_norm = t(gl["final_norm"])

@@ -48,3 +48,20 @@ def test_full_model_tokens_match_golden(cuda, golden_dir):
     # last-step logits against the stored oracle values
     head = np.array(g["last_logits_head"], np.float32)
     assert np.abs(lg1[:16].cpu().numpy() - head).max() <= TOL * g["last_logits_max"]
+
+
+def test_decoder_from_gptq_checkpoint_file(cuda, tmp_path):
+    """The checkpoint route (safetensors file in the GPTQ key naming -> loader -> decoder) gives the
+    same tokens and logits as the in-memory weights it was written from."""
+    from antares_b200 import gptq
+    from antares_b200.llama import synth_globals, synth_layer
+    cfg = LlamaConfig(n_layers=2, max_seq=64)
+    path = str(tmp_path / "model.safetensors")
+    gptq.write_gptq_checkpoint(path, cfg, [synth_layer(cfg, l) for l in range(cfg.n_layers)], synth_globals(cfg))
+    prompt = synth_prompt(cfg, 5, 1)
+    ref = LlamaInt4Decoder(cfg, cuda)
+    want = ref.generate(prompt, 10)
+    want_logits = ref.logits.clone()
+    dec = LlamaInt4Decoder(cfg, cuda, weights=gptq.GptqLlamaWeights(path, cfg))
+    assert list(dec.generate(prompt, 10)) == list(want)
+    assert torch.equal(dec.logits, want_logits)
