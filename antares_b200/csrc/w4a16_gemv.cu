@@ -63,7 +63,7 @@ __device__ __forceinline__ void issue_prefetch_hint(const GemvParams &p) {
 // recomputes the row's sum of squares from L2: 16 KiB for K = 4096); SiLU(gate) * up of an fp16
 // [M, 2K] row.
 template <int M, int EPI, int PRO>
-__global__ void __launch_bounds__(GEMV_THREADS, (M == 1) ? 4 : 1) w4a16_gemv_f16_kernel(GemvParams p) {
+__global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned cs = cluster.num_blocks(), krank = cluster.block_rank();
