@@ -44,6 +44,11 @@ struct GemvParams {
   const unsigned char *pf[2] = {nullptr, nullptr};
   unsigned pf_bytes[2] = {0, 0};
   int pdl_late = 0;  // release the dependent kernel after the streaming loop instead of at the start
+  // Weight addressing (int32 words / halves): row stride and offset of a 128-column tile.  The
+  // reference layout [K/8, N] has ld = N, tile = 128; the tile-major layout [N/128][K/8][128]
+  // (each CTA's weights contiguous in HBM) has ld = 128, tile = (K/8) * 128.  0 = reference layout.
+  unsigned ld_w = 0, ld_s = 0;
+  size_t tile_w = 0, tile_s = 0;
 };
 
 constexpr unsigned PF_CHUNK = 16 * 1024;
@@ -84,15 +89,18 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
   // predicate: out-of-range columns are clamped to the last valid chunk and dropped at the store).
   const int n0c = col_ok ? n0 : p.N - 4;
   int u = u_begin + warp;
-  const unsigned row_step = (unsigned)p.N / 4;                      // uint4 elements between packed rows
-  const uint4 *wp = reinterpret_cast<const uint4 *>(p.qw + (size_t)u * UNIT_ROWS * p.N + n0c);
+  const unsigned ld_w = p.ld_w ? p.ld_w : (unsigned)p.N, ld_s = p.ld_s ? p.ld_s : (unsigned)p.N;
+  const size_t tile_w = p.ld_w ? p.tile_w : (size_t)TILE_N, tile_s = p.ld_s ? p.tile_s : (size_t)TILE_N;
+  const int cl = n0c - tile * TILE_N;                                // column offset inside the tile
+  const unsigned row_step = ld_w / 4;                                // uint4 elements between packed rows
+  const uint4 *wp = reinterpret_cast<const uint4 *>(p.qw + (size_t)tile * tile_w + (size_t)u * UNIT_ROWS * ld_w + cl);
   const unsigned unit_step = row_step * UNIT_ROWS * GEMV_WARPS;     // to this warp's next unit
   // scales: the warp advances 8 units = 256 k per round; for the usual group sizes that is a whole
   // number of scale rows, otherwise the row is recomputed per unit
   const bool s_fast = (UNIT_K * GEMV_WARPS) % p.group == 0;
-  const unsigned s_step = (unsigned)((UNIT_K * GEMV_WARPS) / p.group) * p.N;
-  const __half *scol = reinterpret_cast<const __half *>(p.scales) + n0c;
-  const __half *sp = scol + (size_t)((u * UNIT_K) / p.group) * p.N;
+  const unsigned s_step = (unsigned)((UNIT_K * GEMV_WARPS) / p.group) * ld_s;
+  const __half *scol = reinterpret_cast<const __half *>(p.scales) + (size_t)tile * tile_s + cl;
+  const __half *sp = scol + (size_t)((u * UNIT_K) / p.group) * ld_s;
 
   constexpr int NBUF = 2;  // units in flight per warp (registers)
   uint4 wbuf[NBUF][UNIT_ROWS];
@@ -105,7 +113,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     wp += unit_step;
     u_load += GEMV_WARPS;
     if (s_fast) sp += s_step;
-    else sp = scol + (size_t)((u_load * UNIT_K) / p.group) * p.N;
+    else sp = scol + (size_t)((u_load * UNIT_K) / p.group) * ld_s;
   };
 
   if (!p.pdl_late) pdl_launch_dependents();
@@ -715,6 +723,26 @@ extern "C" int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *n
                 "w4a16_gemv_fused: workspace must be 16-byte aligned and hold %zu bytes", gemv_persist_scratch_bytes(M, K, N));
   return gemv_f16(x, prologue, reinterpret_cast<const __half *>(norm_weight_f16), eps, qweight, scales, out, M, K, N, group, epilogue,
                   workspace, (cudaStream_t)stream);
+}
+
+extern "C" int ab200_w4a16_gemv_tiled(const void *x, int prologue, const void *norm_weight_f16, float eps, const int32_t *qweight_tiled,
+                                      const void *scales_tiled, void *out, int epilogue, int M, int K, int N, int group, void *stream) {
+  clear_error();
+  if (int rc = check_gemv_args(x, qweight_tiled, scales_tiled, out, M, K, N, group)) return rc;
+  AB200_REQUIRE(prologue >= 0 && prologue <= 2 && epilogue >= 0 && epilogue <= 2, "w4a16_gemv_tiled: bad prologue %d / epilogue %d", prologue, epilogue);
+  AB200_REQUIRE(prologue != PRO_RMSNORM || norm_weight_f16 != nullptr, "w4a16_gemv_tiled: RMSNorm prologue needs a weight vector");
+  AB200_REQUIRE(N % TILE_N == 0, "w4a16_gemv_tiled: N=%d must be a multiple of %d for the tile-major layout", N, TILE_N);
+  AB200_REQUIRE(M <= 4, "w4a16_gemv_tiled: batch %d (the tile-major path serves batches of 1-4 rows)", M);
+  GemvParams p{x, qweight_tiled, scales_tiled, out, K, N, group, K / UNIT_K, 0};
+  p.norm_w = reinterpret_cast<const __half *>(norm_weight_f16);
+  p.eps = eps;
+  p.ld_w = TILE_N;
+  p.ld_s = TILE_N;
+  p.tile_w = (size_t)(K / 8) * TILE_N;
+  p.tile_s = (size_t)(K / group) * TILE_N;
+  if (prologue == PRO_PLAIN) return gemv_f16_scalar<PRO_PLAIN>(p, M, epilogue, (cudaStream_t)stream);
+  if (prologue == PRO_RMSNORM) return gemv_f16_scalar<PRO_RMSNORM>(p, M, epilogue, (cudaStream_t)stream);
+  return gemv_f16_scalar<PRO_SILU_MUL>(p, M, epilogue, (cudaStream_t)stream);
 }
 
 extern "C" int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream) {

@@ -113,7 +113,7 @@ class LlamaInt4Decoder:
     `weights` selects the checkpoint (gptq.GptqLlamaWeights); None = seeded synthetic weights.
     """
 
-    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None):
+    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None, tiled=True):
         assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
         self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         self.hl = cfg.n_heads // world            # local heads
@@ -127,6 +127,9 @@ class LlamaInt4Decoder:
         for l in range(cfg.n_layers):
             full = weights.layer(l) if weights is not None else synth_layer(cfg, l)
             w = shard_layer(cfg, full, rank, world)
+            if tiled:  # tile-major weights: what one CTA streams is one contiguous range of HBM
+                for k in ("vqk", "o", "gu", "down"):
+                    w[k + "_q"], w[k + "_s"] = packing.tile_weights(w[k + "_q"], w[k + "_s"])
             self.layers.append({k: t(v) for k, v in w.items()})
         gl = weights.globals() if weights is not None else synth_globals(cfg)
         self.embed = t(gl["embed"])
@@ -154,6 +157,7 @@ class LlamaInt4Decoder:
         self.n_prompt = 0
         self.att_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
+        self.tiled = bool(tiled)
         self.launches_per_step = 0
         self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
         self._plist = []
@@ -167,14 +171,19 @@ class LlamaInt4Decoder:
     def _proj(self, x, q, s, out, prologue=0, epilogue=0, norm_w=None):
         """One fused W4A16 projection launch (prologue 0 plain / 1 RMSNorm of the fp32 residual /
         2 SiLU(gate)*up; epilogue 0 fp16 / 1 residual += / 2 fp32 partial)."""
-        K, N = q.shape[0] * 8, q.shape[1]
-        if self.prefetch == 1:
-            # the projection kernel itself pulls the NEXT projection's weights into L2 while it streams
-            nq, ns = self._plist[(self._pi + 1) % len(self._plist)]
-            call("ab200_w4a16_gemv_prefetch_hint", nq.data_ptr(), nq.numel() * 4, ns.data_ptr(), ns.numel() * 2)
-            self._pi += 1
-        call("ab200_w4a16_gemv_fused", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
-             q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, 0, 0, self._st)
+        if self.tiled:  # q: [N/128, K/8, 128]
+            K, N = q.shape[1] * 8, q.shape[0] * q.shape[2]
+            call("ab200_w4a16_gemv_tiled", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
+                 q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, self._st)
+        else:
+            K, N = q.shape[0] * 8, q.shape[1]
+            if self.prefetch == 1:
+                # the projection kernel itself pulls the NEXT projection's weights into L2 while it streams
+                nq, ns = self._plist[(self._pi + 1) % len(self._plist)]
+                call("ab200_w4a16_gemv_prefetch_hint", nq.data_ptr(), nq.numel() * 4, ns.data_ptr(), ns.numel() * 2)
+                self._pi += 1
+            call("ab200_w4a16_gemv_fused", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
+                 q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, 0, 0, self._st)
         self._n += 1
 
     def _row_parallel(self, x, q, s, prologue):

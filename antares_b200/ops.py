@@ -221,3 +221,16 @@ def w4a16_gemv_fused(x, qweight, scales, out, prologue=PRO_PLAIN, epilogue=EPI_F
          _chk(qweight, "qweight", torch.int32), _chk(scales, "scales", torch.float16), _chk(out, "out", want_o), int(epilogue),
          M, K, N, group, ws_ptr, ws_bytes, _stream())
     return out
+
+
+def w4a16_gemv_tiled(x, qweight_tiled, scales_tiled, out, prologue=PRO_PLAIN, epilogue=EPI_F16, norm_weight=None, eps=1e-6, group=128):
+    """w4a16_gemv_fused on tile-major weights (packing.tile_weights): qweight_tiled [N/128, K/8, 128]."""
+    K, N = qweight_tiled.shape[1] * 8, qweight_tiled.shape[0] * qweight_tiled.shape[2]
+    xk = x.shape[-1] // 2 if prologue == PRO_SILU_MUL else x.shape[-1]
+    if xk != K:
+        raise ValueError("x has %d values per row, the weights %d rows" % (xk, K))
+    M = x.numel() // x.shape[-1]
+    call("ab200_w4a16_gemv_tiled", _chk(x, "x"), prologue, 0 if norm_weight is None else _chk(norm_weight, "norm_weight", torch.float16), float(eps),
+         _chk(qweight_tiled, "qweight_tiled", torch.int32), _chk(scales_tiled, "scales_tiled", torch.float16), _chk(out, "out"),
+         epilogue, M, K, N, group, _stream())
+    return out

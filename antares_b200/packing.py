@@ -75,3 +75,15 @@ def shard_rows(qweight, scales, rank, world, group=GROUP):
     K = qweight.shape[0] * 8
     k0, k1 = row_shard_bounds(K, world, group)[rank]
     return (np.ascontiguousarray(qweight[k0 // 8:k1 // 8]), np.ascontiguousarray(scales[k0 // group:k1 // group]), (k0, k1))
+
+
+def tile_weights(qweight, scales, tile=128):
+    """Reference layout qweight [K/8, N], scales [K/group, N] -> tile-major [N/tile][K/8][tile],
+    [N/tile][K/group][tile] (numpy), the layout ab200_w4a16_gemv_tiled streams."""
+    qweight, scales = np.asarray(qweight), np.asarray(scales)
+    n = qweight.shape[1]
+    if n % tile:
+        raise ValueError("N=%d is not a multiple of %d" % (n, tile))
+    q = np.ascontiguousarray(qweight.reshape(qweight.shape[0], n // tile, tile).transpose(1, 0, 2))
+    s = np.ascontiguousarray(scales.reshape(scales.shape[0], n // tile, tile).transpose(1, 0, 2))
+    return q, s

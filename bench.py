@@ -228,7 +228,6 @@ def run_reference(args, as_baseline=False):
 
 def gemv_roofline(dec, torch, peak_gbs, peak_kind):
     """Device time of the step's W4A16 GEMV launches alone (same weights, same order, as a graph)."""
-    from antares_b200._lib import call
     cfg = dec.cfg
     side = torch.cuda.Stream(device=dec.dev)
     n_launch, alg = 0, 0
@@ -236,16 +235,15 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
     def enqueue():
         nonlocal n_launch, alg
         n_launch, alg = 0, 0
-        st = torch.cuda.current_stream().cuda_stream
+        dec._st = torch.cuda.current_stream().cuda_stream
+        dec._n = dec._pi = 0
         for w in dec.layers:
             # the step's four projections with their fused prologues/epilogues (scratch buffers as outputs)
-            for x, q, s, out, pro, epi, nw in ((dec.x, w["vqk_q"], w["vqk_s"], dec.vqk, 1, 0, w["att_norm"]),
-                                               (dec.att, w["o_q"], w["o_s"], dec.partial, 0, 2, None),
-                                               (dec.x, w["gu_q"], w["gu_s"], dec.gu, 1, 0, w["ffn_norm"]),
-                                               (dec.gu, w["down_q"], w["down_s"], dec.partial, 2, 2, None)):
-                K, N = q.shape[0] * 8, q.shape[1]
-                call("ab200_w4a16_gemv_fused", x.data_ptr(), pro, 0 if nw is None else nw.data_ptr(), cfg.eps, q.data_ptr(),
-                     s.data_ptr(), out.data_ptr(), epi, 1, K, N, cfg.group, 0, 0, st)
+            for x, k, out, pro, epi, nw, K, N in ((dec.x, "vqk", dec.vqk, 1, 0, w["att_norm"], cfg.dim, 3 * dec.dl),
+                                                  (dec.att, "o", dec.partial, 0, 2, None, dec.dl, cfg.dim),
+                                                  (dec.x, "gu", dec.gu, 1, 0, w["ffn_norm"], cfg.dim, 2 * dec.fl),
+                                                  (dec.gu, "down", dec.partial, 2, 2, None, dec.fl, cfg.dim)):
+                dec._proj(x, w[k + "_q"], w[k + "_s"], out, pro, epi, nw)
                 n_launch += 1
                 alg += K * N // 2 + (K // cfg.group) * N * 2 + K * 2 + N * 2
 
@@ -358,7 +356,7 @@ def run_ours(args):
         _ops.set_option("pdl", args.pdl)
     cfg = LlamaConfig(max_seq=N_PROMPT + W + K + 8)
     dec = LlamaInt4Decoder(cfg, dev, rank=rank, world=world, comm=comm, max_tokens=N_PROMPT + W + K + 8,
-                           prefetch=args.prefetch)
+                           prefetch=args.prefetch, tiled=not args.reference_layout)
     prompt = synth_prompt(cfg, N_PROMPT, 0)
     dec.prompt[:N_PROMPT].copy_(torch.from_numpy(prompt))
     dec.capture(N_PROMPT)
@@ -417,7 +415,8 @@ def run_ours(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "llama2-7b-arch int4 g128 greedy decode, batch 1, %d prompt tokens then %d timed tokens" % (N_PROMPT, K),
                        "parallelism": "tp%d" % world, "allreduce": ("none" if world == 1 else args.comm), "l2": "each step streams %.2f GB of weights per GPU (> L2), no flush needed" % (step_bytes / 1e9),
-                       "launcher": "cuda graph, 1 replay per token"},
+                       "launcher": "cuda graph, 1 replay per token",
+                       "weight_layout": "reference [K/8, N]" if args.reference_layout else "tile-major [N/128][K/8][128] (repacked at load)"},
             "e2e": {"value": K / sec_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": dec.launches_per_step * K, "launches_per_step": dec.launches_per_step,
             "clocks": clocks, "roofline": roof,
@@ -449,6 +448,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the operator-level figures (prefill GEMM, GEMV set)")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 release dependents at kernel start, 2 after the GEMV streaming loop")
+    ap.add_argument("--reference-layout", action="store_true", help="keep the weights in the reference's [K/8, N] layout instead of tile-major")
     ap.add_argument("--prefetch", type=int, default=0, help="1: every projection kernel also pulls the next one's weights into L2 (measured neutral)")
     ap.add_argument("--comm", default="push", choices=["push", "nccl"], help="all-reduce of row-parallel partials: one-shot NVLink push kernel or NCCL")
     args = ap.parse_args()

@@ -121,6 +121,18 @@ int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_
                            void *stream);
 size_t ab200_w4a16_gemv_workspace_bytes(int M, int K, int N);
 
+/* ab200_w4a16_gemv_fused on weights stored TILE-MAJOR, the layout this library prefers in HBM:
+ *   qweight_tiled int32 [N/128][K/8][128]   (tile t, packed row r, column c  <-  qweight[r][128 t + c])
+ *   scales_tiled  fp16  [N/128][K/group][128]
+ * so that the weights one CTA streams are one contiguous range (the reference layout [K/8, N]
+ * gives it 512-byte pieces 4 N bytes apart).  Same arithmetic, same results bit for bit.  N must
+ * be a multiple of 128, batch 1..4, fp16.  antares_b200.packing.tile_weights() produces the
+ * layout from the reference's.  No counterpart in the reference (its layout is fixed by the
+ * checkpoint format, samples/05_llama2_7b_int4.py:22-29). */
+int ab200_w4a16_gemv_tiled(const void *x, int prologue, const void *norm_weight_f16, float eps,
+                           const int32_t *qweight_tiled, const void *scales_tiled, void *out,
+                           int epilogue, int M, int K, int N, int group, void *stream);
+
 /* ab200_w4a16_gemv for callers that may not allocate device memory.  No counterpart in the
  * reference.  Some hosts hand a plugin no way to allocate: an inference server that reserves the
  * whole device for its own memory pool at start-up and forbids driver allocations afterwards

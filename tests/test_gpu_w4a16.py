@@ -250,3 +250,33 @@ def test_dependent_chain_is_identical_under_programmatic_launch(cuda, impl):
         ops.set_option("gemv_impl", 0)
     assert torch.isfinite(results[0].float()).all()
     assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (1, 4096, 22016), (2, 11008, 4096), (4, 256, 128)])
+def test_tile_major_layout_gives_identical_results(cuda, M, K, N):
+    """The tile-major weight layout ([N/128][K/8][128], what the decoder keeps in HBM) changes only
+    addresses: results equal the reference layout's bit for bit, for every prologue/epilogue."""
+    qw, sc = packing.synth_w4(K, N, 51)
+    qt, st = packing.tile_weights(qw, sc)
+    assert qt.shape == (N // 128, K // 8, 128) and np.array_equal(qt[1, 3, :], qw[3, 128:256]) if N > 128 else True
+    rng = np.random.default_rng(52)
+    x16 = _dev(packing.synth_x(M, K, 53), cuda)
+    x32 = _dev((rng.standard_normal((M, K)) * 3).astype(np.float32), cuda)
+    gu = _dev(rng.standard_normal((M, 2 * K)).astype(np.float16), cuda)
+    wn = _dev((1 + 0.1 * rng.standard_normal(K)).astype(np.float16), cuda)
+    dq, ds, dqt, dst = _dev(qw, cuda), _dev(sc, cuda), _dev(qt, cuda), _dev(st, cuda)
+    ops.set_option("gemv_impl", 1)  # same kernel on both sides: only the addressing differs
+    try:
+        for xin, pro, nw in ((x16, ops.PRO_PLAIN, None), (x32, ops.PRO_RMSNORM, wn), (gu, ops.PRO_SILU_MUL, None)):
+            for epi, dt in ((ops.EPI_F16, torch.float16), (ops.EPI_RESIDUAL, torch.float32)):
+                a = torch.ones((M, N), dtype=dt, device=cuda)
+                b = torch.ones((M, N), dtype=dt, device=cuda)
+                ops.w4a16_gemv_fused(xin, dq, ds, a, prologue=pro, epilogue=epi, norm_weight=nw)
+                ops.w4a16_gemv_tiled(xin, dqt, dst, b, prologue=pro, epilogue=epi, norm_weight=nw)
+                assert torch.equal(a, b), (pro, epi)
+    finally:
+        ops.set_option("gemv_impl", 0)
+    ref = cport.w4a16_gemm(packing.synth_x(M, K, 53), qw, sc)
+    y = torch.empty((M, N), dtype=torch.float16, device=cuda)
+    ops.w4a16_gemv_tiled(x16, dqt, dst, y)
+    assert _err(y.cpu().numpy(), ref) <= TOL

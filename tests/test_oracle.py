@@ -119,3 +119,15 @@ def test_row_shards_cover_k():
     assert np.allclose(acc, full, rtol=1e-4, atol=1e-4)
     cols = [cport.np_w4a16_gemm(x, *[a.astype(np.float32) if a.dtype == np.float16 else a for a in packing.shard_columns(qw, sc, r, 4)]) for r in range(4)]
     assert np.allclose(np.concatenate(cols, axis=1), full, rtol=1e-5, atol=1e-5)
+
+
+def test_tile_major_repacking_is_a_pure_permutation():
+    """packing.tile_weights: tile t holds columns 128 t .. 128 t + 127 of every packed row / scale row."""
+    from antares_b200 import packing
+    qw, sc = packing.synth_w4(256, 384, 1)
+    qt, st = packing.tile_weights(qw, sc)
+    assert qt.shape == (3, 32, 128) and st.shape == (3, 2, 128)
+    for t in range(3):
+        assert np.array_equal(qt[t], qw[:, t * 128:(t + 1) * 128]) and np.array_equal(st[t], sc[:, t * 128:(t + 1) * 128])
+    with pytest.raises(ValueError):
+        packing.tile_weights(qw[:, :100], sc[:, :100])
