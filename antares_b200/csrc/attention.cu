@@ -47,8 +47,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *
   float *red = att_smem + max_seq;    // [16][128]
   __shared__ float sh[32];
   const int h = blockIdx.x;
-  int S = *seq_len_dev + seq_len_add;
+  // blockIdx.y = query row of a causal prefill: row r sees r more cache rows than row 0
+  int S = *seq_len_dev + seq_len_add + (int)blockIdx.y;
   S = S < 0 ? 0 : (S > max_seq ? max_seq : S);
+  q += (size_t)blockIdx.y * gridDim.x * ATT_D;
+  out += (size_t)blockIdx.y * gridDim.x * ATT_D;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 15, hw = lane >> 4;
 
@@ -408,5 +411,24 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
   AB200_CUDA(cudaLaunchKernelEx(&cfg, attention_fused_kernel, p));
+  return AB200_OK;
+}
+
+// Causal attention of `rows` consecutive tokens over a cache that already holds their keys and
+// values: query row r (position *pos0_dev + r) attends cache rows 0 .. *pos0_dev + r.  The batched
+// form of ab200_attention_decode (grid = heads x rows).
+extern "C" int ab200_attention_prefill(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16, const int32_t *pos0_dev,
+                                       int rows, int max_seq, int H, int D, long kv_stride, float scale, void *stream) {
+  clear_error();
+  AB200_REQUIRE(q_f16 && k_cache_f16 && v_cache_f16 && out_f16 && pos0_dev && rows > 0 && rows <= 65535, "attention_prefill: bad argument");
+  AB200_REQUIRE(D == ATT_D, "attention_prefill: head size %d is not the built size %d", D, ATT_D);
+  AB200_REQUIRE(H > 0 && max_seq > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0, "attention_prefill: bad shape H=%d max_seq=%d kv_stride=%ld", H, max_seq, kv_stride);
+  AB200_REQUIRE(aligned16(q_f16) && aligned16(k_cache_f16) && aligned16(v_cache_f16) && aligned16(out_f16), "attention_prefill: pointers must be 16-byte aligned");
+  const size_t smem = ((size_t)max_seq + 16 * ATT_D) * sizeof(float);
+  if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_prefill: max_seq=%d exceeds the shared-memory score buffer", max_seq);
+  if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  attention_decode_kernel<__half><<<dim3(H, rows), ATT_THREADS, smem, (cudaStream_t)stream>>>(
+      (const __half *)q_f16, (const __half *)k_cache_f16, (const __half *)v_cache_f16, (__half *)out_f16, pos0_dev, 1, max_seq, kv_stride, scale);
+  AB200_CHECK_LAUNCH("attention_prefill");
   return AB200_OK;
 }

@@ -205,6 +205,8 @@ __global__ void __launch_bounds__(ROW_THREADS) softmax_rows_kernel(const T *__re
 
 // ---- decode-step glue ------------------------------------------------------------------------------
 __global__ void silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ out, int n) {
+  gu += (size_t)blockIdx.y * 2 * n;  // one row of [gate | up] per blockIdx.y
+  out += (size_t)blockIdx.y * n;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n / 8; i += gridDim.x * blockDim.x) {
     float g[8], u[8];
     load8<__half>(gu + (size_t)i * 8, g);
@@ -217,7 +219,8 @@ __global__ void silu_mul_kernel(const __half *__restrict__ gu, __half *__restric
 
 __global__ void embed_lookup_kernel(const __half *__restrict__ embed, const int32_t *__restrict__ token,
                                     float *__restrict__ x, int dim, int vocab) {
-  int t = *token;
+  int t = token[blockIdx.y];  // one token per blockIdx.y
+  x += (size_t)blockIdx.y * dim;
   t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
     x[i] = __half2float(embed[(size_t)t * dim + i]);
@@ -228,9 +231,11 @@ __global__ void __launch_bounds__(ROW_THREADS) rope_kv_store_kernel(const __half
                                                                    const int32_t *__restrict__ pos_dev, __half *__restrict__ q_out,
                                                                    __half *__restrict__ kc, __half *__restrict__ vc, int H, int D,
                                                                    long kv_stride, int max_seq) {
-  const int pos = *pos_dev;
+  const int pos = *pos_dev + (int)blockIdx.x;  // one token per block: positions pos, pos + 1, ...
   if (pos < 0 || pos >= max_seq) return;  // out-of-range step: leave the cache untouched
   const int HD = H * D, half = D / 2, chunks = half / 8;
+  vqk += (size_t)blockIdx.x * 3 * HD;
+  q_out += (size_t)blockIdx.x * HD;
   const __half *v = vqk, *q = vqk + HD, *k = vqk + 2 * HD;
   __half *krow = kc + (size_t)pos * kv_stride, *vrow = vc + (size_t)pos * kv_stride;
   for (int i = threadIdx.x; i < HD / 8; i += ROW_THREADS)
@@ -254,6 +259,19 @@ __global__ void __launch_bounds__(ROW_THREADS) rope_kv_store_kernel(const __half
     for (int j = 0; j < 8; ++j) { oa[j] = a[j] * c[j] - b[j] * s[j]; ob[j] = b[j] * c[j] + a[j] * s[j]; }
     store8<__half>(krow + base, oa);
     store8<__half>(krow + base + half, ob);
+  }
+}
+
+// x_f32[i] += y_f16[i]: residual update after a prefill GEMM (fp16 output, fp32 residual stream).
+__global__ void residual_add_f16_kernel(float *__restrict__ x, const __half *__restrict__ y, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    float f[8];
+    load8<__half>(y + i * 8, f);
+    float4 a = *reinterpret_cast<float4 *>(x + i * 8), b = *reinterpret_cast<float4 *>(x + i * 8 + 4);
+    a.x += f[0]; a.y += f[1]; a.z += f[2]; a.w += f[3];
+    b.x += f[4]; b.y += f[5]; b.z += f[6]; b.w += f[7];
+    *reinterpret_cast<float4 *>(x + i * 8) = a;
+    *reinterpret_cast<float4 *>(x + i * 8 + 4) = b;
   }
 }
 
@@ -440,5 +458,47 @@ extern "C" int ab200_greedy_next(const float *logits_f32, int n, const int32_t *
   AB200_REQUIRE(logits_f32 && token_dev && pos_dev && n > 0, "greedy_next: bad argument");
   greedy_next_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(logits_f32, n, prompt, n_prompt, token_dev, pos_dev, out_tokens);
   AB200_CHECK_LAUNCH("greedy_next");
+  return AB200_OK;
+}
+
+// ---- batched (prefill) forms of the decode-step glue: one row per prompt token ---------------------
+
+extern "C" int ab200_embed_rows(const void *embed_f16, const int32_t *tokens_dev, float *x_f32, int rows, int dim, int vocab, void *stream) {
+  clear_error();
+  AB200_REQUIRE(embed_f16 && tokens_dev && x_f32 && rows > 0 && rows <= 65535 && dim > 0 && vocab > 0, "embed_rows: bad argument");
+  embed_lookup_kernel<<<dim3(grid1d(dim, 256), rows), 256, 0, (cudaStream_t)stream>>>((const __half *)embed_f16, tokens_dev, x_f32, dim, vocab);
+  AB200_CHECK_LAUNCH("embed_rows");
+  return AB200_OK;
+}
+
+extern "C" int ab200_rope_kv_store_rows(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev, void *q_out_f16, void *k_cache_f16,
+                                        void *v_cache_f16, int rows, int H, int D, long kv_stride, int max_seq, void *stream) {
+  clear_error();
+  AB200_REQUIRE(vqk_f16 && inv_freq && pos0_dev && q_out_f16 && k_cache_f16 && v_cache_f16 && rows > 0, "rope_kv_store_rows: bad argument");
+  AB200_REQUIRE(D > 0 && D % 16 == 0 && D / 16 <= ROW_THREADS && H > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0,
+                "rope_kv_store_rows: bad shape H=%d D=%d kv_stride=%ld", H, D, kv_stride);
+  AB200_REQUIRE(aligned16(vqk_f16) && aligned16(q_out_f16) && aligned16(k_cache_f16) && aligned16(v_cache_f16),
+                "rope_kv_store_rows: pointers must be 16-byte aligned");
+  rope_kv_store_kernel<<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)vqk_f16, inv_freq, pos0_dev, (__half *)q_out_f16,
+                                                                     (__half *)k_cache_f16, (__half *)v_cache_f16, H, D, kv_stride, max_seq);
+  AB200_CHECK_LAUNCH("rope_kv_store_rows");
+  return AB200_OK;
+}
+
+extern "C" int ab200_silu_mul_rows(const void *gate_up_f16, void *out_f16, int rows, int n, void *stream) {
+  clear_error();
+  AB200_REQUIRE(gate_up_f16 && out_f16 && rows > 0 && rows <= 65535 && n > 0 && n % 8 == 0, "silu_mul_rows: n=%d must be a positive multiple of 8", n);
+  AB200_REQUIRE(aligned16(gate_up_f16) && aligned16(out_f16), "silu_mul_rows: pointers must be 16-byte aligned");
+  silu_mul_kernel<<<dim3(grid1d(n / 8, 128), rows), 128, 0, (cudaStream_t)stream>>>((const __half *)gate_up_f16, (__half *)out_f16, n);
+  AB200_CHECK_LAUNCH("silu_mul_rows");
+  return AB200_OK;
+}
+
+extern "C" int ab200_residual_add_f16(float *x_f32, const void *y_f16, size_t n, void *stream) {
+  clear_error();
+  AB200_REQUIRE(x_f32 && y_f16 && n > 0 && n % 8 == 0, "residual_add_f16: n must be a positive multiple of 8");
+  AB200_REQUIRE(aligned16(x_f32) && aligned16(y_f16), "residual_add_f16: pointers must be 16-byte aligned");
+  residual_add_f16_kernel<<<grid1d(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(x_f32, (const __half *)y_f16, n / 8);
+  AB200_CHECK_LAUNCH("residual_add_f16");
   return AB200_OK;
 }

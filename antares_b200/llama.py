@@ -157,6 +157,7 @@ class LlamaInt4Decoder:
         self.n_prompt = 0
         self.att_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
+        self._ref_cache = {}
         self.tiled = bool(tiled)
         self.launches_per_step = 0
         self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
@@ -232,6 +233,68 @@ class LlamaInt4Decoder:
         self._n += 1
         self.launches_per_step = self._n
 
+    # -- batched prefill -------------------------------------------------------------------------------
+    def _ref_layout(self, l, k):
+        """Weights of projection k of layer l in the checkpoint's [K/8, N] layout (what the prefill GEMM
+        takes); made once, on the device, from the tile-major copies the decode kernels stream."""
+        key = (l, k)
+        if key not in self._ref_cache:
+            q, s = self.layers[l][k + "_q"], self.layers[l][k + "_s"]
+            if self.tiled:
+                q = q.permute(1, 0, 2).reshape(q.shape[1], -1).contiguous()
+                s = s.permute(1, 0, 2).reshape(s.shape[1], -1).contiguous()
+            self._ref_cache[key] = (q, s)
+        return self._ref_cache[key]
+
+    def prefill(self, prompt):
+        """Runs the whole prompt through the model in one pass (every projection is one tensor-core
+        GEMM over all prompt tokens, attention is causal over the freshly written cache rows) instead
+        of token by token as the reference does (samples/05_llama2_7b_int4.py:194-200).  Leaves the
+        decoder exactly where token-by-token feeding would: cache rows 0..T-1 filled, pos = T,
+        token = the first generated token.  Returns that token (int).  Single GPU only."""
+        if self.world != 1:
+            raise NotImplementedError("batched prefill is implemented for one GPU (tensor-parallel runs feed the prompt through the decode step)")
+        cfg = self.cfg
+        prompt = np.asarray(prompt, np.int32)
+        T = int(len(prompt))
+        assert 1 <= T <= cfg.max_seq and T <= self.max_tokens
+        dev, st = self.dev, torch.cuda.current_stream().cuda_stream
+        self.reset(torch.from_numpy(prompt).to(dev))
+        toks = self.prompt[:T]
+        d, f = cfg.dim, self.fl
+        h16 = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)
+        x = torch.empty(T, d, dtype=torch.float32, device=dev)
+        xb, vqk, q, att, o, gu, hh = h16(T, d), h16(T, 3 * d), h16(T, d), h16(T, d), h16(T, d), h16(T, 2 * f), h16(T, f)
+        call("ab200_embed_rows", self.embed.data_ptr(), toks.data_ptr(), x.data_ptr(), T, d, cfg.vocab, st)
+
+        def gemm(a, l, k, out):
+            qw, sc = self._ref_layout(l, k)
+            call("ab200_w4a16_gemm", a.data_ptr(), qw.data_ptr(), sc.data_ptr(), out.data_ptr(), T, qw.shape[0] * 8, qw.shape[1], cfg.group, 0, st)
+
+        for l, w in enumerate(self.layers):
+            call("ab200_rmsnorm", x.data_ptr(), 1, w["att_norm"].data_ptr(), xb.data_ptr(), T, d, cfg.eps, st)
+            gemm(xb, l, "vqk", vqk)
+            call("ab200_rope_kv_store_rows", vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), q.data_ptr(),
+                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), T, self.hl, cfg.head_dim, self.dl, cfg.max_seq, st)
+            call("ab200_attention_prefill", q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), att.data_ptr(),
+                 self.pos.data_ptr(), T, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
+            gemm(att, l, "o", o)
+            call("ab200_residual_add_f16", x.data_ptr(), o.data_ptr(), T * d, st)
+            call("ab200_rmsnorm", x.data_ptr(), 1, w["ffn_norm"].data_ptr(), xb.data_ptr(), T, d, cfg.eps, st)
+            gemm(xb, l, "gu", gu)
+            call("ab200_silu_mul_rows", gu.data_ptr(), hh.data_ptr(), T, f, st)
+            gemm(hh, l, "down", o)
+            call("ab200_residual_add_f16", x.data_ptr(), o.data_ptr(), T * d, st)
+        # classifier on the last token only, then the same bookkeeping as a decode step at pos = T - 1
+        self.x.copy_(x[T - 1])
+        self.pos.fill_(T - 1)
+        call("ab200_rmsnorm", self.x.data_ptr(), 1, self.final_norm.data_ptr(), self.xb.data_ptr(), 1, d, cfg.eps, st)
+        call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), d, self.vl, st)
+        call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), T, self.token.data_ptr(), self.pos.data_ptr(),
+             self.out_tokens.data_ptr(), st)
+        self.out_tokens[:T].copy_(toks)
+        return int(self.token.item())
+
     # -- graph ---------------------------------------------------------------------------------------
     def capture(self, n_prompt):
         """Captures one step as a CUDA graph.  n_prompt is baked into the graph (the argmax kernel
@@ -262,9 +325,10 @@ class LlamaInt4Decoder:
         self.out_tokens.zero_()
         self.out_tokens[:1].copy_(self.prompt[:1])
 
-    def generate(self, prompt, n_new):
-        """Feeds the prompt token by token (as the reference does, lines 194-200) and generates
-        n_new tokens greedily.  Returns all n_prompt + n_new token ids (numpy)."""
+    def generate(self, prompt, n_new, batched_prefill=False):
+        """Generates n_new tokens greedily after the prompt.  By default the prompt is fed token by
+        token through the decode step (as the reference does, lines 194-200); with batched_prefill
+        it goes through prefill() in one pass.  Returns all n_prompt + n_new token ids (numpy)."""
         prompt = np.asarray(prompt, np.int32)
         n_prompt = len(prompt)
         total = n_prompt + n_new
@@ -272,9 +336,14 @@ class LlamaInt4Decoder:
         if self.graph is None or self._n_prompt_capture != n_prompt:
             self.prompt[:n_prompt].copy_(torch.from_numpy(prompt))
             self.capture(n_prompt)
-        self.reset(torch.from_numpy(prompt).to(self.dev))
-        for _ in range(total - 1):
-            self.graph.replay()
+        if batched_prefill and n_new >= 1:
+            self.prefill(prompt)                 # produces the first new token
+            for _ in range(n_new - 1):
+                self.graph.replay()
+        else:
+            self.reset(torch.from_numpy(prompt).to(self.dev))
+            for _ in range(total - 1):
+                self.graph.replay()
         torch.cuda.synchronize()
         return self.out_tokens[:total].cpu().numpy()
 

@@ -40,7 +40,7 @@ UNIT = "tokens/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up GEMV launch (K=4096, N=22016, M=1) from the
 # ncu capture summarised in profiles/w4a16_gemv_scalar_gate_up_m1.md (algorithmic bytes: 46,550,016).
-NCU_TRAFFIC_GATE_UP = 46533888 + 2560
+NCU_TRAFFIC_GATE_UP = 46535168 + 1280  # dram__bytes_read.sum + dram__bytes_write.sum of one gate|up launch (profiles/w4a16_gemv_scalar_gate_up_m1.md)
 
 
 def measured_peaks():
@@ -431,9 +431,29 @@ def run_ours(args):
         if os.path.exists(path):
             with open(path) as f:
                 tensor_peak = float(json.load(f).get("bf16_tflops", tensor_peak))
+        # time to first token for the 128-token prompt: the reference's way (token by token through
+        # the decode step) and the batched prefill (tensor-core GEMMs over all prompt tokens)
+        ttft = {}
+        for name in ("token_by_token", "batched_prefill"):
+            best = None
+            for _ in range(3):
+                fence()
+                t0 = time.perf_counter()
+                if name == "batched_prefill":
+                    dec.prefill(prompt)
+                else:
+                    dec.reset(torch.from_numpy(prompt).to(dev))
+                    for _ in range(N_PROMPT):
+                        dec.graph.replay()
+                fence()
+                dt = (time.perf_counter() - t0) * 1e3
+                best = dt if best is None else min(best, dt)
+            ttft[name + "_ms"] = best
+            ttft[name + "_first_token"] = int(dec.token.item())
         del dec
         torch.cuda.empty_cache()
         line["extras"] = extras_single_ops(torch, dev, peak, tensor_peak)
+        line["extras"]["time_to_first_token_128"] = ttft
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = run_reference(argparse.Namespace(steps=20, warmup=0, gpus=1), as_baseline=True)
     return line

@@ -232,6 +232,26 @@ int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, in
 int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
                       int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
 
+/* ---- batched (prefill) forms of the glue above: one row per prompt token.  The reference feeds the
+ * prompt token by token through the decode step (samples/05_llama2_7b_int4.py:194-200); these let
+ * the whole prompt go through ab200_w4a16_gemm instead. ---- */
+
+/* x_f32[r, :] = embed_f16[tokens_dev[r], :]. */
+int ab200_embed_rows(const void *embed_f16, const int32_t *tokens_dev, float *x_f32, int rows,
+                     int dim, int vocab, void *stream);
+/* ab200_rope_kv_store for rows consecutive tokens: vqk [rows, 3*H*D], positions *pos0_dev + r. */
+int ab200_rope_kv_store_rows(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev,
+                             void *q_out_f16, void *k_cache_f16, void *v_cache_f16, int rows, int H,
+                             int D, long kv_stride, int max_seq, void *stream);
+/* Causal attention: query row r (position *pos0_dev + r) attends cache rows 0 .. *pos0_dev + r. */
+int ab200_attention_prefill(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16,
+                            void *out_f16, const int32_t *pos0_dev, int rows, int max_seq, int H,
+                            int D, long kv_stride, float scale, void *stream);
+/* out[r, i] = silu(gate_up[r, i]) * gate_up[r, n + i]. */
+int ab200_silu_mul_rows(const void *gate_up_f16, void *out_f16, int rows, int n, void *stream);
+/* x_f32[i] += y_f16[i] (residual update after a prefill GEMM). */
+int ab200_residual_add_f16(float *x_f32, const void *y_f16, size_t n, void *stream);
+
 /* One-shot hint for the calling thread's NEXT fp16 ab200_w4a16_gemv* call: while that kernel
  * streams its own weights, one thread per CTA also asks for the two byte ranges (normally the
  * following projection's qweight and scales) to be pulled into L2, so HBM stays busy across the
