@@ -280,3 +280,32 @@ def test_tile_major_layout_gives_identical_results(cuda, M, K, N):
     y = torch.empty((M, N), dtype=torch.float16, device=cuda)
     ops.w4a16_gemv_tiled(x16, dqt, dst, y)
     assert _err(y.cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 4])
+@pytest.mark.parametrize("kind", ["offset", "outlier", "tiny", "huge"])
+def test_gemv_accuracy_on_awkward_activations(cuda, impl, kind):
+    """The raw-nibble multiply takes the zero-point out of the inner sum and (scalar kernel) scales
+    each activation row by a power of two: activations with a large common offset, a single large
+    outlier, very small or very large magnitudes must stay inside the tolerance."""
+    K, N = 4096, 4096
+    qw, sc = packing.synth_w4(K, N, 61)
+    rng = np.random.default_rng(62)
+    x = rng.standard_normal((2, K))
+    if kind == "offset":
+        x = 10 + x
+    elif kind == "outlier":
+        x[:, 7] = 300.0
+    elif kind == "tiny":
+        x = x * 1e-4
+    else:
+        x = x * 2e3
+    x = x.astype(np.float16)
+    ref = cport.w4a16_gemm(x, qw, sc)
+    ops.set_option("gemv_impl", impl)
+    try:
+        y = ops.w4a16_gemv(_dev(x, cuda), _dev(qw, cuda), _dev(sc, cuda)).cpu().numpy()
+    finally:
+        ops.set_option("gemv_impl", 0)
+    assert np.isfinite(y.astype(np.float32)).all()
+    assert _err(y, ref) <= TOL
