@@ -47,6 +47,7 @@ SIGNATURES = {
     "ab200_attention_prefill": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],
     "ab200_silu_mul_rows": [_vp, _vp, _i, _i, _vp],
     "ab200_residual_add_f16": [_vp, _vp, _sz, _vp],
+    "ab200_greedy_next_tp_emulated": [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp],
     "ab200_greedy_next_tp": [_vp, _i, _i, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp],
     "ab200_w4a16_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],

@@ -101,14 +101,12 @@ __global__ void __launch_bounds__(COMM_THREADS) allreduce_residual_kernel(CommPe
 // pairs per rank), every rank picks the same winner (highest value, lowest index on ties, like
 // torch.argmax over the gathered logits) and does the loop bookkeeping of the single-GPU
 // greedy_next kernel.  Replaces the logits all-gather + argmax of the classifier step.
-__global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_kernel(CommPeers c, const float *__restrict__ logits, int n, int vocab_offset,
-                                                                      const int32_t *__restrict__ prompt, int n_prompt, int32_t *token_dev,
-                                                                      int32_t *pos_dev, int32_t *out_tokens) {
+__device__ __forceinline__ void greedy_next_tp_body(const CommPeers &c, const float *__restrict__ logits, int n, int vocab_offset,
+                                                    const int32_t *__restrict__ prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,
+                                                    int32_t *out_tokens) {
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sh_fail;
-  pdl_launch_dependents();
-  pdl_wait();
   float best = -CUDART_INF_F;
   int bi = 0x7fffffff;
   const int nvec = ((reinterpret_cast<uintptr_t>(logits) & 15u) == 0) ? n / 4 : 0;
@@ -186,6 +184,27 @@ __global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_kernel(CommPeers 
     *pos_dev = pos + 1;
     *c.epoch = e;
   }
+}
+
+__global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_kernel(CommPeers c, const float *__restrict__ logits, int n, int vocab_offset,
+                                                                      const int32_t *__restrict__ prompt, int n_prompt, int32_t *token_dev,
+                                                                      int32_t *pos_dev, int32_t *out_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  greedy_next_tp_body(c, logits, n, vocab_offset, prompt, n_prompt, token_dev, pos_dev, out_tokens);
+}
+
+// All ranks of the greedy exchange as the blocks of one cooperative launch (single-GPU protocol check).
+struct GreedyEmu {
+  CommPeers peers[COMM_MAX_WORLD];
+  const float *logits[COMM_MAX_WORLD];
+  int n[COMM_MAX_WORLD], offset[COMM_MAX_WORLD];
+  int32_t *token[COMM_MAX_WORLD], *pos[COMM_MAX_WORLD], *out_tokens[COMM_MAX_WORLD];
+};
+__global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_emulated_kernel(const GreedyEmu *emu, const int32_t *prompt, int n_prompt) {
+  const int r = blockIdx.x;
+  const CommPeers c = emu->peers[r];
+  greedy_next_tp_body(c, emu->logits[r], emu->n[r], emu->offset[r], prompt, n_prompt, emu->token[r], emu->pos[r], emu->out_tokens[r]);
 }
 
 // All ranks in one launch on one GPU (rank = blockIdx.x): the protocol check for machines with
@@ -289,7 +308,32 @@ extern "C" int ab200_allreduce_residual_emulated(float *const *x_host, const flo
   return AB200_OK;
 }
 
-extern "C" size_t ab200_comm_emulation_scratch_bytes(void) { return sizeof(CommEmu); }
+extern "C" size_t ab200_comm_emulation_scratch_bytes(void) { return sizeof(CommEmu) > sizeof(GreedyEmu) ? sizeof(CommEmu) : sizeof(GreedyEmu); }
+
+extern "C" int ab200_greedy_next_tp_emulated(const float *const *logits_host, const int *n_local_host, const int *offset_host, void *const *bufs_host,
+                                             int world, int n_max, const int32_t *prompt, int n_prompt, int32_t *const *token_host,
+                                             int32_t *const *pos_host, int32_t *const *out_tokens_host, void *emu_scratch_dev, void *stream) {
+  clear_error();
+  AB200_REQUIRE(logits_host && n_local_host && offset_host && bufs_host && token_host && pos_host && out_tokens_host && emu_scratch_dev,
+                "greedy_next_tp_emulated: null pointer");
+  AB200_REQUIRE(world >= 1 && world <= COMM_MAX_WORLD && n_max >= 4 && n_max % 4 == 0, "greedy_next_tp_emulated: bad sizes");
+  GreedyEmu emu{};
+  for (int r = 0; r < world; ++r) {
+    fill_peers(emu.peers[r], bufs_host, r, world, n_max);
+    emu.logits[r] = logits_host[r];
+    emu.n[r] = n_local_host[r];
+    emu.offset[r] = offset_host[r];
+    emu.token[r] = token_host[r];
+    emu.pos[r] = pos_host[r];
+    emu.out_tokens[r] = out_tokens_host[r];
+  }
+  AB200_CUDA(cudaMemcpyAsync(emu_scratch_dev, &emu, sizeof(emu), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  AB200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));  // `emu` is a stack object
+  const GreedyEmu *dev_emu = reinterpret_cast<const GreedyEmu *>(emu_scratch_dev);
+  void *args[] = {(void *)&dev_emu, (void *)&prompt, (void *)&n_prompt};
+  AB200_CUDA(cudaLaunchCooperativeKernel((void *)greedy_next_tp_emulated_kernel, dim3(world), dim3(COMM_THREADS), args, 0, (cudaStream_t)stream));
+  return AB200_OK;
+}
 
 extern "C" int ab200_greedy_next_tp(const float *logits_local_f32, int n_local, int vocab_offset, void *const *bufs_host, int rank, int world,
                                     int n_max, const int32_t *prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,

@@ -303,6 +303,13 @@ int ab200_allreduce_residual_emulated(float *const *x_host, const float *const *
                                       void *const *bufs_host, int world, int n_max,
                                       void *emu_scratch_dev, void *stream);
 size_t ab200_comm_emulation_scratch_bytes(void);
+/* ab200_greedy_next_tp with all ranks as the blocks of one cooperative launch on one GPU (per-rank
+ * host arrays of device pointers): the protocol check for machines with fewer GPUs than ranks. */
+int ab200_greedy_next_tp_emulated(const float *const *logits_host, const int *n_local_host,
+                                  const int *offset_host, void *const *bufs_host, int world, int n_max,
+                                  const int32_t *prompt, int n_prompt, int32_t *const *token_host,
+                                  int32_t *const *pos_host, int32_t *const *out_tokens_host,
+                                  void *emu_scratch_dev, void *stream);
 
 #ifdef __cplusplus
 }

@@ -75,3 +75,46 @@ def test_wait_for_a_missing_peer_runs_out_and_is_reported(cuda):
         ops.set_option("comm_wait_polls", 1 << 24)
         for b in bufs:
             call("ab200_comm_free", b)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_emulated_vocabulary_parallel_greedy_step(cuda, world):
+    """Every rank holds a shard of the logits; after the candidate exchange all ranks pick the token
+    torch.argmax picks on the gathered logits (lowest index on ties), advance the position and log
+    the token - over several steps (both slot sets), with a tie placed across two shards."""
+    vl = 1000
+    bufs = [_alloc(world, 4) for _ in range(world)]
+    try:
+        L = _lib.load()
+        scratch = torch.zeros(int(L.ab200_comm_emulation_scratch_bytes()), dtype=torch.uint8, device=cuda)
+        rng = np.random.default_rng(world)
+        tok = [torch.zeros(1, dtype=torch.int32, device=cuda) for _ in range(world)]
+        pos = [torch.zeros(1, dtype=torch.int32, device=cuda) for _ in range(world)]
+        outs = [torch.zeros(16, dtype=torch.int32, device=cuda) for _ in range(world)]
+        prompt = torch.tensor([5, 6], dtype=torch.int32, device=cuda)  # position 1 is forced to prompt[1]
+        P = ctypes.c_void_p
+        arr = lambda xs: ctypes.cast((P * world)(*xs), P)
+        n_arr = (ctypes.c_int * world)(*([vl] * world))
+        off_arr = (ctypes.c_int * world)(*[r * vl for r in range(world)])
+        want = []
+        for step in range(5):
+            full = rng.standard_normal(world * vl).astype(np.float32)
+            if step == 2:  # the same maximum in the last shard and in shard 0: the lower index must win
+                full[world * vl - 3] = 9.0
+                full[17] = 9.0
+            shards = [torch.from_numpy(full[r * vl:(r + 1) * vl].copy()).to(cuda) for r in range(world)]
+            call("ab200_greedy_next_tp_emulated", arr([t.data_ptr() for t in shards]), ctypes.cast(n_arr, P), ctypes.cast(off_arr, P),
+                 arr(bufs), world, 4, prompt.data_ptr(), 2, arr([t.data_ptr() for t in tok]), arr([t.data_ptr() for t in pos]),
+                 arr([t.data_ptr() for t in outs]), scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            expect = 6 if step == 0 else int(np.argmax(full))
+            want.append(expect)
+            for r in range(world):
+                assert int(tok[r].item()) == expect and int(pos[r].item()) == step + 1, (step, r)
+        assert want[2] == 17
+        for r in range(world):
+            assert outs[r][1:6].cpu().tolist() == want
+        assert ops.kernel_status() == 0
+    finally:
+        for b in bufs:
+            call("ab200_comm_free", b)
