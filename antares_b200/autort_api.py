@@ -13,7 +13,8 @@ Calling convention kept: tensors positionally in declared order; the result is r
 written into a trailing positional tensor / `out=`; scalars come through `extra=[...]`; dimensions
 declared `Name:val` are upper bounds, the call may pass fewer elements (README.md:64-67).
 `config=` carries tuner hints in the reference ("tune:5", "~N~:[256,8,32],..."): the kernels here
-are hand-scheduled, so it is accepted and ignored.  IR outside the built operator family raises
+are hand-scheduled, so it is accepted and ignored.  Single element-wise statements outside the named
+family run on a generic interpreter kernel (ir.compile_elementwise); other IR raises
 NotImplementedError; nothing runs on the CPU.
 """
 import torch
@@ -84,6 +85,21 @@ def export(ir, inputs, config=None, name=None):
         def fn(*tensors, out=None, extra=None):
             t, out = _split_call(match, tensors, out)
             return _ops.softmax(t[match.params["x"]], out=out)
+    elif match.kind == "eltwise":
+        pr = match.params
+
+        def fn(*tensors, out=None, extra=None):
+            t, out = _split_call(match, tensors, out)
+            ins = [t[n] for n in pr["inputs"]]
+            shape = ins[0].shape
+            for n, a in zip(pr["inputs"], ins):
+                if a.shape != shape:
+                    raise ValueError("%s: element-wise inputs must have one shape (%s has %s, expected %s)" % (match.name, n, tuple(a.shape), tuple(shape)))
+            if out is None:
+                # result dtype: the widest input dtype, as the reference's promotion rule gives (lang/einstein_v2.py:26-32)
+                dt = torch.float32 if any(a.dtype == torch.float32 for a in ins) else torch.float16
+                out = torch.empty(shape, dtype=dt, device=ins[0].device)
+            return _ops.eltwise_program(pr["program"], pr["consts"], ins, out=out)
     else:  # pragma: no cover - recognise() raises first
         raise NotImplementedError(match.kind)
     fn.__name__ = match.name

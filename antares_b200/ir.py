@@ -29,7 +29,7 @@ class TensorSpec:
 
 @dataclass
 class OpMatch:
-    kind: str                       # "w4a16" | "sigmoid" | "softmax"
+    kind: str                       # "w4a16" | "sigmoid" | "softmax" | "eltwise"
     name: str                       # exported op name
     inputs: list                    # TensorSpec in declared order
     output: str                     # l-value tensor of the last statement
@@ -118,6 +118,236 @@ def recognise(ir, inputs, name=None):
             if by_name[m.group(3)].dtype not in ("float16", "float32"):
                 raise NotImplementedError("sigmoid: float16 or float32 only")
             return OpMatch("sigmoid", op_name, specs, m.group(1), dict(x=m.group(3), dtype=by_name[m.group(3)].dtype))
+    if len(stmts) == 1:
+        # any other single element-wise statement: the interpreter kernel
+        try:
+            out_name, axes, used, prog, consts = compile_elementwise(stmts[0], [s.name for s in specs])
+        except NotImplementedError as e:
+            reason = str(e)
+        else:
+            bad = [n for n in used if by_name[n].dtype not in ("float16", "float32")]
+            if not bad and all(len(by_name[n].dims) == len(axes) for n in used):
+                return OpMatch("eltwise", name or out_name, specs, out_name, dict(inputs=used, program=prog, consts=consts, axes=axes))
+            reason = "element-wise IR: inputs must be float16/float32 tensors of the output's rank"
+    else:
+        reason = "multi-statement programs other than the W4A16 and softmax forms are not supported"
     raise NotImplementedError(
-        "this IR is outside the hand-written operator family (W4A16 dequant-matmul, sigmoid, row softmax); "
-        "antares_b200 has no general code generator and no fallback:\n  " + "\n  ".join(stmts))
+        "this IR is outside the operator family (W4A16 dequant-matmul, sigmoid, row softmax, single element-wise statements); "
+        "antares_b200 has no general code generator and no fallback (%s):\n  " % reason + "\n  ".join(stmts))
+
+
+# ---- general element-wise statements -------------------------------------------------------------------
+# `out[A, B] = expr` where every tensor in expr is indexed by exactly the output's axis list.  The
+# expression is compiled to a small stack program that one CUDA kernel interprets (csrc/eltwise_vm.cu):
+# the generic route for fusions outside the named operator family (lang/einstein_v2.py:297-578 is the
+# reference's general front end; this covers its element-wise subset: + - * /, unary minus, numeric
+# constants, .call(`f`) / .call(strs.f) with the functions below, .call(`max`|`min`|`pow`, [expr]),
+# and dtype casts, which are no-ops here because the interpreter computes in fp32).
+
+VM_OPS = {"in": 0, "const": 1, "add": 2, "sub": 3, "mul": 4, "div": 5, "neg": 6, "exp": 7, "log": 8, "sqrt": 9, "rsqrt": 10,
+          "tanh": 11, "erf": 12, "sin": 13, "cos": 14, "abs": 15, "floor": 16, "ceil": 17, "max": 18, "min": 19, "pow": 20,
+          "sigmoid": 21}
+_VM_UNARY = ("exp", "log", "sqrt", "rsqrt", "tanh", "erf", "sin", "cos", "abs", "floor", "ceil", "sigmoid")
+_VM_BINARY_CALL = ("max", "min", "pow")
+VM_MAX_OPS, VM_MAX_CONSTS, VM_MAX_INPUTS, VM_MAX_STACK = 48, 16, 8, 8
+
+_TOKEN = re.compile(r"\s*(?:(\d+\.\d*(?:[eE][-+]?\d+)?|\.\d+(?:[eE][-+]?\d+)?|\d+(?:[eE][-+]?\d+)?)|([A-Za-z_]\w*)|(`[^`]*`)|(.))")
+
+
+def _tokenise(text):
+    out, pos = [], 0
+    while pos < len(text):
+        m = _TOKEN.match(text, pos)
+        if not m:
+            break
+        pos = m.end()
+        num, ident, quoted, sym = m.groups()
+        if num is not None:
+            out.append(("num", num))
+        elif ident is not None:
+            out.append(("id", ident))
+        elif quoted is not None:
+            out.append(("str", quoted[1:-1]))
+        elif sym and not sym.isspace():
+            out.append(("sym", sym))
+    return out
+
+
+class _EltParser:
+    def __init__(self, tokens, axes, input_names):
+        self.t, self.i, self.axes, self.names = tokens, 0, axes, input_names
+        self.prog, self.consts, self.used = [], [], []
+        self.depth = self.max_depth = 0
+
+    def peek(self):
+        return self.t[self.i] if self.i < len(self.t) else ("end", "")
+
+    def take(self, kind=None, val=None):
+        k, v = self.peek()
+        if (kind and k != kind) or (val is not None and v != val):
+            raise NotImplementedError("element-wise IR: expected %s %r, found %r" % (kind or "", val or "", v))
+        self.i += 1
+        return v
+
+    def emit(self, op, arg=0, delta=0):
+        self.prog.append((VM_OPS[op], arg))
+        self.depth += delta
+        self.max_depth = max(self.max_depth, self.depth)
+
+    def expr(self):
+        self.term()
+        while self.peek() in (("sym", "+"), ("sym", "-")):
+            op = self.take()
+            self.term()
+            self.emit("add" if op == "+" else "sub", delta=-1)
+
+    def term(self):
+        self.unary()
+        while self.peek() in (("sym", "*"), ("sym", "/")):
+            op = self.take()
+            self.unary()
+            self.emit("mul" if op == "*" else "div", delta=-1)
+
+    def unary(self):
+        if self.peek() == ("sym", "-"):
+            self.take()
+            self.unary()
+            self.emit("neg")
+        else:
+            self.postfix()
+
+    def postfix(self):
+        self.primary()
+        while self.peek() == ("sym", "."):
+            self.take()
+            method = self.take("id")
+            self.take("sym", "(")
+            if method == "call":
+                fname = self.func_name()
+                if self.peek() == ("sym", ","):
+                    self.take()
+                    self.take("sym", "[")
+                    self.expr()
+                    self.take("sym", "]")
+                    if fname not in _VM_BINARY_CALL:
+                        raise NotImplementedError("element-wise IR: %s takes no second operand" % fname)
+                    self.emit(fname, delta=-1)
+                elif fname in _VM_UNARY:
+                    self.emit(fname)
+                else:
+                    raise NotImplementedError("element-wise IR: function %r is not supported" % fname)
+                self.take("sym", ")")
+            elif method in ("cast", "to", "like"):  # dtype changes: the interpreter computes in fp32
+                depth = 1
+                while depth:
+                    k, v = self.peek()
+                    if k == "end":
+                        raise NotImplementedError("element-wise IR: unbalanced parentheses")
+                    self.i += 1
+                    depth += (v == "(") - (v == ")") if k == "sym" else 0
+            else:
+                raise NotImplementedError("element-wise IR: method .%s() is not supported" % method)
+
+    def func_name(self):
+        k, v = self.peek()
+        if k == "str":
+            self.take()
+            return v
+        if k == "id" and v == "strs":
+            self.take()
+            self.take("sym", ".")
+            return self.take("id")
+        raise NotImplementedError("element-wise IR: .call() needs `name` or strs.name")
+
+    def primary(self):
+        k, v = self.peek()
+        if k == "num":
+            self.take()
+            self.const(float(v))
+        elif k == "sym" and v == "(":
+            self.take()
+            self.expr()
+            self.take("sym", ")")
+        elif k == "id" and v == "const":
+            self.take()
+            self.take("sym", "(")
+            neg = self.peek() == ("sym", "-")
+            if neg:
+                self.take()
+            self.const((-1 if neg else 1) * float(self.take("num")))
+            self.take("sym", ")")
+        elif k == "id":
+            self.take()
+            if v not in self.names:
+                raise NotImplementedError("element-wise IR: %r is not a declared input" % v)
+            self.take("sym", "[")
+            idx = []
+            while self.peek() != ("sym", "]"):
+                kk, vv = self.peek()
+                self.take()
+                if kk == "id":
+                    idx.append(vv)
+                elif not (kk == "sym" and vv == ","):
+                    raise NotImplementedError("element-wise IR: only plain axis indices are supported")
+            self.take("sym", "]")
+            if idx != self.axes:
+                raise NotImplementedError("element-wise IR: %s is indexed by %s, the output by %s" % (v, idx, self.axes))
+            if v not in self.used:
+                self.used.append(v)
+            self.emit("in", self.used.index(v), delta=1)
+        else:
+            raise NotImplementedError("element-wise IR: unexpected %r" % v)
+
+    def const(self, c):
+        if c not in self.consts:
+            self.consts.append(c)
+        self.emit("const", self.consts.index(c), delta=1)
+
+
+def compile_elementwise(stmt, input_names):
+    """'out[N] = expr' -> (output name, axes, input names in stack-program order, program, constants).
+    Raises NotImplementedError when the statement is not purely element-wise."""
+    m = re.match(r"^\s*([a-z_]\w*)\s*\[([^\]]*)\]\s*=(?!=)(.*)$", stmt, re.S)
+    if not m:
+        raise NotImplementedError("element-wise IR: not an assignment: %r" % stmt)
+    out_name, axes_text, rhs = m.groups()
+    axes = [a.strip() for a in axes_text.split(",") if a.strip()]
+    if not axes or not all(re.fullmatch(r"[A-Z]\w*", a) for a in axes):
+        raise NotImplementedError("element-wise IR: the output must be indexed by plain axes")
+    p = _EltParser(_tokenise(rhs), axes, list(input_names))
+    p.expr()
+    if p.peek()[0] != "end":
+        raise NotImplementedError("element-wise IR: trailing text %r" % (p.peek()[1],))
+    if len(p.prog) > VM_MAX_OPS or len(p.consts) > VM_MAX_CONSTS or len(p.used) > VM_MAX_INPUTS or p.max_depth > VM_MAX_STACK:
+        raise NotImplementedError("element-wise IR: expression too large for the interpreter (%d ops, %d constants, %d inputs, depth %d)"
+                                  % (len(p.prog), len(p.consts), len(p.used), p.max_depth))
+    if not p.used:
+        raise NotImplementedError("element-wise IR: the expression reads no input tensor")
+    return out_name, axes, p.used, p.prog, p.consts
+
+
+def eval_program_numpy(prog, consts, arrays):
+    """Reference evaluation of a stack program (numpy, fp32), for the host-side tests."""
+    import numpy as np
+    from math import erf as _erf
+    inv = {v: k for k, v in VM_OPS.items()}
+    st = []
+    f32 = np.float32
+    for op, arg in prog:
+        name = inv[op]
+        if name == "in":
+            st.append(np.asarray(arrays[arg], dtype=f32))
+        elif name == "const":
+            st.append(f32(consts[arg]))
+        elif name in ("add", "sub", "mul", "div", "max", "min", "pow"):
+            b, a = st.pop(), st.pop()
+            st.append({"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide, "max": np.maximum, "min": np.minimum,
+                       "pow": np.power}[name](a, b).astype(f32))
+        else:
+            a = st.pop()
+            fn = {"neg": np.negative, "exp": np.exp, "log": np.log, "sqrt": np.sqrt, "rsqrt": lambda v: 1 / np.sqrt(v), "tanh": np.tanh,
+                  "erf": np.vectorize(_erf, otypes=[f32]), "sin": np.sin, "cos": np.cos, "abs": np.abs, "floor": np.floor, "ceil": np.ceil,
+                  "sigmoid": lambda v: 1 / (1 + np.exp(-v))}[name]
+            st.append(np.asarray(fn(a), dtype=f32))
+    assert len(st) == 1
+    return st[0]

@@ -234,3 +234,24 @@ def w4a16_gemv_tiled(x, qweight_tiled, scales_tiled, out, prologue=PRO_PLAIN, ep
          _chk(qweight_tiled, "qweight_tiled", torch.int32), _chk(scales_tiled, "scales_tiled", torch.float16), _chk(out, "out"),
          epilogue, M, K, N, group, _stream())
     return out
+
+
+def eltwise_program(prog, consts, inputs, out=None, out_dtype=None):
+    """Runs a stack program (ir.compile_elementwise) over same-sized fp16/fp32 tensors."""
+    import ctypes
+    n = inputs[0].numel()
+    for t in inputs:
+        if t.numel() != n:
+            raise ValueError("element-wise inputs must all hold %d elements" % n)
+    if out is None:
+        out = torch.empty_like(inputs[0], dtype=out_dtype or inputs[0].dtype)
+    elif out.numel() != n:
+        raise ValueError("out must hold %d elements" % n)
+    ops_b = (ctypes.c_ubyte * len(prog))(*[int(o) for o, _ in prog])
+    args_b = (ctypes.c_ubyte * len(prog))(*[int(a) for _, a in prog])
+    cst = (ctypes.c_float * max(1, len(consts)))(*[float(c) for c in consts])
+    ptrs = (ctypes.c_void_p * len(inputs))(*[_chk(t, "input") for t in inputs])
+    dts = (ctypes.c_int * len(inputs))(*[_code(t.dtype) for t in inputs])
+    call("ab200_eltwise_vm", ctypes.cast(ops_b, ctypes.c_void_p), ctypes.cast(args_b, ctypes.c_void_p), len(prog), ctypes.cast(cst, ctypes.c_void_p),
+         len(consts), ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(dts, ctypes.c_void_p), len(inputs), _chk(out, "out"), _code(out.dtype), n, _stream())
+    return out

@@ -232,6 +232,20 @@ int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, in
 int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
                       int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
 
+/* Generic element-wise operator: interprets a stack program compiled from an Antares-IR statement
+ * `out[axes] = expr` whose tensors are all indexed by the output's axes (antares_b200/ir.py::
+ * compile_elementwise; the reference generates one kernel per such expression,
+ * lang/einstein_v2.py:297-578).  ops/args: n_ops byte codes with their operand (input or constant
+ * index); operation codes: 0 input, 1 constant, 2 add, 3 sub, 4 mul, 5 div, 6 neg, 7 exp, 8 log,
+ * 9 sqrt, 10 rsqrt, 11 tanh, 12 erf, 13 sin, 14 cos, 15 abs, 16 floor, 17 ceil, 18 max, 19 min,
+ * 20 pow, 21 sigmoid.  At most 48 operations, 16 constants, 8 inputs, stack depth 8; inputs and
+ * output hold n elements of AB200_F16 or AB200_F32; arithmetic in fp32.  The program is
+ * validated on the host (AB200_EINVAL on a malformed one). */
+int ab200_eltwise_vm(const unsigned char *ops_host, const unsigned char *args_host, int n_ops,
+                     const float *consts_host, int n_consts, const void *const *inputs_host,
+                     const int *in_dtypes_host, int n_inputs, void *out, int out_dtype, size_t n,
+                     void *stream);
+
 /* ---- batched (prefill) forms of the glue above: one row per prompt token.  The reference feeds the
  * prompt token by token through the decode step (samples/05_llama2_7b_int4.py:194-200); these let
  * the whole prompt go through ab200_w4a16_gemm instead. ---- */

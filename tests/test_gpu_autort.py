@@ -100,3 +100,37 @@ def test_legacy_custom_op_binding(cuda):
     assert torch.allclose(sm(xs), torch.softmax(xs, -1), atol=1e-6)
     with pytest.raises(NotImplementedError):
         CustomOp(ir="output0[N] = input0[N] + input1[N]", input_orders={"input0": xs[0], "input1": xs[1]}, device=dev).emit()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [4096 * 33, 1001])
+def test_exported_elementwise_statements_run_on_the_interpreter(cuda, dtype, n):
+    """autort.export of single element-wise statements outside the named family (the reference
+    compiles a kernel per statement): tanh-GELU, a fused scaled residual, and a two-input
+    expression with max/abs/rsqrt, against numpy in fp32."""
+    import autort
+    from antares_b200 import ir
+    dt = "float32" if dtype == torch.float32 else "float16"
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal(n).astype(np.float32)
+    y = (rng.standard_normal(n) * 2).astype(np.float32)
+    xd, yd = torch.from_numpy(x).to(cuda).to(dtype), torch.from_numpy(y).to(cuda).to(dtype)
+    xr, yr = xd.float().cpu().numpy(), yd.float().cpu().numpy()
+    tol = 1e-5 if dtype == torch.float32 else 2e-3
+    gelu = autort.export(ir="out[N] = 0.5 * x[N] * (1.0 + (0.7978845608 * (x[N] + 0.044715 * x[N] * x[N] * x[N])).call(`tanh`))",
+                         inputs=["x=%s[N:%d]" % (dt, 1 << 22)], name="gelu_tanh")
+    assert gelu.match.kind == "eltwise"
+    got = autort.ops.gelu_tanh(xd).float().cpu().numpy()
+    want = 0.5 * xr * (1 + np.tanh(0.7978845608 * (xr + 0.044715 * xr ** 3)))
+    assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())
+    fused = autort.export(ir="z[N] = a[N] + 0.125 * (b[N] - a[N]).call(strs.max, [const(0.0)]) * (b[N].call(`abs`) + 1.0).call(`rsqrt`)",
+                          inputs=["a=%s[N:%d]" % (dt, 1 << 22), "b=%s[N:%d]" % (dt, 1 << 22)])
+    out = torch.empty(n, dtype=dtype, device=cuda)
+    fused(xd, yd, out)                       # trailing output tensor, as samples/05_llama2_7b_int4.py:157 passes it
+    want = xr + 0.125 * np.maximum(yr - xr, 0) / np.sqrt(np.abs(yr) + 1)
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * max(1.0, np.abs(want).max())
+    # an odd offset view (not 16-byte aligned) takes the scalar path
+    if n > 8:
+        got = autort.ops.gelu_tanh(xd[1:]).float().cpu().numpy()
+        want = 0.5 * xr[1:] * (1 + np.tanh(0.7978845608 * (xr[1:] + 0.044715 * xr[1:] ** 3)))
+        assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())

@@ -44,9 +44,41 @@ def test_recognises_sigmoid_and_softmax():
 
 
 def test_everything_else_is_refused_not_emulated():
-    with pytest.raises(NotImplementedError):
-        ir.recognise("output0[N] = input0[N] + input1[N]", ["input0=float32[8]", "input1=float32[8]"])
+    with pytest.raises(NotImplementedError):   # a matmul: neither W4A16 nor element-wise
+        ir.recognise("output0[N, M] +=! input0[N, K] * input1[K, M]", ["input0=float32[8, 8]", "input1=float32[8, 8]"])
+    with pytest.raises(NotImplementedError):   # integer element-wise (the interpreter computes in fp32)
+        ir.recognise("output0[N] = input0[N] + input1[N]", ["input0=int32[8]", "input1=int32[8]"])
     with pytest.raises(NotImplementedError):   # zero-point other than 8
         ir.recognise(W4A16_IR.replace("- 8)", "- 7)"), W4A16_INPUTS)
     with pytest.raises(NotImplementedError):   # mixed dtypes
         ir.recognise(W4A16_IR, ["input0=float16[S:4096]", "qweight=int32[L:512, N:12288]", "scales=float32[K:32, N:12288]"])
+
+
+def test_elementwise_statements_compile_to_stack_programs():
+    """Single element-wise statements outside the named family go to the interpreter: the stack
+    program evaluates to the expression (numpy), constants are pooled, casts are no-ops."""
+    import numpy as np
+    from antares_b200 import ir
+    gelu = "out[N] = 0.5 * x[N] * (1.0 + (0.7978845608 * (x[N] + 0.044715 * x[N] * x[N] * x[N])).call(`tanh`))"
+    m = ir.recognise(gelu, ["x=float32[N:4096]"])
+    assert m.kind == "eltwise" and m.name == "out" and m.params["inputs"] == ["x"]
+    x = np.linspace(-4, 4, 33).astype(np.float32)
+    got = ir.eval_program_numpy(m.params["program"], m.params["consts"], [x])
+    assert np.allclose(got, 0.5 * x * (1 + np.tanh(0.7978845608 * (x + 0.044715 * x ** 3))), atol=1e-6)
+    m = ir.recognise("y[A, B] = (a[A, B] - b[A, B]).call(strs.max, [const(0.0)]) / -c[A, B].cast(`float32`) + a[A, B]",
+                     ["a=float16[8, 16]", "b=float16[8, 16]", "c=float32[8, 16]"], name="fused")
+    assert m.kind == "eltwise" and m.name == "fused" and m.params["inputs"] == ["a", "b", "c"] and m.params["axes"] == ["A", "B"]
+    rng = np.random.default_rng(0)
+    a, b, c = (rng.standard_normal((8, 16)).astype(np.float32) for _ in range(3))
+    got = ir.eval_program_numpy(m.params["program"], m.params["consts"], [a, b, c])
+    assert np.allclose(got, np.maximum(a - b, 0) / -c + a, rtol=1e-6)
+
+
+@pytest.mark.parametrize("bad", ["out[N] = x[N + 1] * 2.0",                 # shifted index: not element-wise
+                                 "out[N] = x[N].call(`frobnicate`)",        # unknown function
+                                 "out[N] +=! x[N, M]",                      # a reduction
+                                 "out[N] = 1.0"])                           # reads nothing
+def test_non_elementwise_statements_are_refused(bad):
+    from antares_b200 import ir
+    with pytest.raises(NotImplementedError):
+        ir.recognise(bad, ["x=float32[N:64]"])
