@@ -136,7 +136,6 @@ struct AttnFusedParams {
   int H, max_seq;
   long kv_stride;
   float scale;
-  int rows_per_cta;       // ceil(max_seq / SPLITS): capacity of the score buffer
 };
 
 constexpr int ATT_PF = 4;  // cache rows per thread fetched before the current token's q/k/v exist
@@ -392,10 +391,8 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   int splits = 1;
   while (splits < 8 && H * splits * 2 <= 2 * sm_count()) splits *= 2;  // up to ~2 CTAs per SM, at most 8 per head
   AttnFusedParams p{(const __half *)vqk_f16, inv_freq, pos_dev, (__half *)k_cache_f16, (__half *)v_cache_f16, (__half *)out_f16,
-                    H, max_seq, kv_stride, scale, (max_seq + splits - 1) / splits};
+                    H, max_seq, kv_stride, scale};
   const size_t smem = ((size_t)16 * ATT_D + ATT_D + 2 * 8) * sizeof(float);
-  if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_fused: max_seq=%d exceeds the shared-memory score buffer", max_seq);
-  if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(H * splits, 1, 1);
   cfg.blockDim = dim3(ATT_THREADS, 1, 1);

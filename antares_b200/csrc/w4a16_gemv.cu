@@ -571,8 +571,6 @@ static int library_scratch(size_t bytes, void **out) {
   AB200_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
   if (g_scratch_bytes[dev] < bytes) {
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    (void)cap;
     size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
     if (g_scratch[dev]) {
       AB200_CUDA(cudaDeviceSynchronize());
