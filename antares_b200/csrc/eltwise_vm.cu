@@ -5,7 +5,8 @@
 // generates a kernel per expression (lang/einstein_v2.py:297-578 -> antares/default_codegen.py);
 // here one kernel serves them all, so no compiler is needed at run time.
 //
-// The operand stack lives in shared memory ([slot][thread] float4: conflict-free); the program
+// The top of the operand stack stays in registers, the rest lives in shared memory ([slot][thread]
+// float4: conflict-free); the program
 // and constants are kernel parameters (uniform loads, one uniform branch per operation, shared
 // by the four elements).  Inputs and output may be fp16 or fp32; 16-byte / 8-byte accesses when
 // the element count and pointers allow, a scalar tail otherwise.
@@ -64,49 +65,50 @@ __global__ void __launch_bounds__(VM_THREADS) eltwise_vm_kernel(const __grid_con
   for (size_t q = (size_t)blockIdx.x * VM_THREADS + threadIdx.x; q < n4; q += (size_t)gridDim.x * VM_THREADS) {
     const size_t i = q * 4;
     const bool vec = vec_ok && (i + 4 <= p.n);
-    int sp = 0;
+    // the top of the stack stays in registers; shared memory holds what is underneath it
+    int sp = 0;  // entries in shared memory
+    float4 top = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < p.n_ops; ++k) {
       const int op = p.op[k], arg = p.arg[k];
-      if (op == VM_IN) {
-        st[sp++][threadIdx.x] = vm_load4(p.in[arg], p.in_f16[arg], i, p.n, vec);
-      } else if (op == VM_CONST) {
-        const float c = p.cst[arg];
-        st[sp++][threadIdx.x] = make_float4(c, c, c, c);
-      } else if (op <= VM_DIV || op >= VM_MAX && op <= VM_POW) {
-        const float4 b = st[--sp][threadIdx.x], a = st[sp - 1][threadIdx.x];
-        float4 r;
-        switch (op) {
-          case VM_ADD: r = zip4(a, b, [](float x, float y) { return x + y; }); break;
-          case VM_SUB: r = zip4(a, b, [](float x, float y) { return x - y; }); break;
-          case VM_MUL: r = zip4(a, b, [](float x, float y) { return x * y; }); break;
-          case VM_DIV: r = zip4(a, b, [](float x, float y) { return x / y; }); break;
-          case VM_MAX: r = zip4(a, b, [](float x, float y) { return fmaxf(x, y); }); break;
-          case VM_MIN: r = zip4(a, b, [](float x, float y) { return fminf(x, y); }); break;
-          default: r = zip4(a, b, [](float x, float y) { return powf(x, y); }); break;
+      if (op <= VM_CONST) {
+        if (k > 0) st[sp++][threadIdx.x] = top;
+        if (op == VM_IN) {
+          top = vm_load4(p.in[arg], p.in_f16[arg], i, p.n, vec);
+        } else {
+          const float c = p.cst[arg];
+          top = make_float4(c, c, c, c);
         }
-        st[sp - 1][threadIdx.x] = r;
+      } else if (op <= VM_DIV || (op >= VM_MAX && op <= VM_POW)) {
+        const float4 b = top, a = st[--sp][threadIdx.x];
+        switch (op) {
+          case VM_ADD: top = zip4(a, b, [](float x, float y) { return x + y; }); break;
+          case VM_SUB: top = zip4(a, b, [](float x, float y) { return x - y; }); break;
+          case VM_MUL: top = zip4(a, b, [](float x, float y) { return x * y; }); break;
+          case VM_DIV: top = zip4(a, b, [](float x, float y) { return x / y; }); break;
+          case VM_MAX: top = zip4(a, b, [](float x, float y) { return fmaxf(x, y); }); break;
+          case VM_MIN: top = zip4(a, b, [](float x, float y) { return fminf(x, y); }); break;
+          default: top = zip4(a, b, [](float x, float y) { return powf(x, y); }); break;
+        }
       } else {
-        const float4 a = st[sp - 1][threadIdx.x];
-        float4 r;
+        const float4 a = top;
         switch (op) {
-          case VM_NEG: r = map4(a, [](float x) { return -x; }); break;
-          case VM_EXP: r = map4(a, [](float x) { return expf(x); }); break;
-          case VM_LOG: r = map4(a, [](float x) { return logf(x); }); break;
-          case VM_SQRT: r = map4(a, [](float x) { return sqrtf(x); }); break;
-          case VM_RSQRT: r = map4(a, [](float x) { return rsqrtf(x); }); break;
-          case VM_TANH: r = map4(a, [](float x) { return tanhf(x); }); break;
-          case VM_ERF: r = map4(a, [](float x) { return erff(x); }); break;
-          case VM_SIN: r = map4(a, [](float x) { return sinf(x); }); break;
-          case VM_COS: r = map4(a, [](float x) { return cosf(x); }); break;
-          case VM_ABS: r = map4(a, [](float x) { return fabsf(x); }); break;
-          case VM_FLOOR: r = map4(a, [](float x) { return floorf(x); }); break;
-          case VM_CEIL: r = map4(a, [](float x) { return ceilf(x); }); break;
-          default: r = map4(a, [](float x) { return 1.0f / (1.0f + expf(-x)); }); break;  // VM_SIGMOID
+          case VM_NEG: top = map4(a, [](float x) { return -x; }); break;
+          case VM_EXP: top = map4(a, [](float x) { return expf(x); }); break;
+          case VM_LOG: top = map4(a, [](float x) { return logf(x); }); break;
+          case VM_SQRT: top = map4(a, [](float x) { return sqrtf(x); }); break;
+          case VM_RSQRT: top = map4(a, [](float x) { return rsqrtf(x); }); break;
+          case VM_TANH: top = map4(a, [](float x) { return tanhf(x); }); break;
+          case VM_ERF: top = map4(a, [](float x) { return erff(x); }); break;
+          case VM_SIN: top = map4(a, [](float x) { return sinf(x); }); break;
+          case VM_COS: top = map4(a, [](float x) { return cosf(x); }); break;
+          case VM_ABS: top = map4(a, [](float x) { return fabsf(x); }); break;
+          case VM_FLOOR: top = map4(a, [](float x) { return floorf(x); }); break;
+          case VM_CEIL: top = map4(a, [](float x) { return ceilf(x); }); break;
+          default: top = map4(a, [](float x) { return 1.0f / (1.0f + expf(-x)); }); break;  // VM_SIGMOID
         }
-        st[sp - 1][threadIdx.x] = r;
       }
     }
-    const float4 r = st[0][threadIdx.x];
+    const float4 r = top;
     if (vec) {
       if (p.out_f16) {
         uint2 h;

@@ -56,4 +56,8 @@ class CustomOp(torch.nn.Module):
             return _ops.sigmoid(t[pr["x"]])
         if self.match.kind == "softmax":
             return _ops.softmax(t[pr["x"]])
+        if self.match.kind == "eltwise":
+            ins = [t[n] for n in pr["inputs"]]
+            dt = torch.float32 if any(a.dtype == torch.float32 for a in ins) else torch.float16
+            return _ops.eltwise_program(pr["program"], pr["consts"], ins, out=torch.empty(ins[0].shape, dtype=dt, device=ins[0].device))
         raise NotImplementedError(self.match.kind)

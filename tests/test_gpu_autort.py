@@ -98,8 +98,10 @@ def test_legacy_custom_op_binding(cuda):
                   input_orders={"input0": (None, torch.float32, [32, 1024])}, device=dev).emit()
     xs = torch.randn(32, 1024, device=dev)
     assert torch.allclose(sm(xs), torch.softmax(xs, -1), atol=1e-6)
-    with pytest.raises(NotImplementedError):
-        CustomOp(ir="output0[N] = input0[N] + input1[N]", input_orders={"input0": xs[0], "input1": xs[1]}, device=dev).emit()
+    add = CustomOp(ir="output0[N] = input0[N] + input1[N]", input_orders={"input0": xs[0], "input1": xs[1]}, device=dev).emit()
+    assert torch.equal(add(xs[0], xs[1]), xs[0] + xs[1])       # a plain element-wise statement: the interpreter kernel
+    with pytest.raises(NotImplementedError):                    # a dense matmul is outside the operator family
+        CustomOp(ir="output0[N, M] +=! input0[N, K] * input1[K, M]", input_orders={"input0": xs, "input1": xs.t().contiguous()}, device=dev).emit()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
