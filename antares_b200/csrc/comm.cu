@@ -55,38 +55,30 @@ __device__ __forceinline__ void allreduce_residual_body(const CommPeers &c, floa
       asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 2), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
     }
   }
-  // 2. collect the peers' pairs from my own buffer: the loads for all peers are issued together
-  //    (one memory round trip per poll, not one per peer), 3. sum in rank order, residual update
+  // 2. collect the peers' pairs from my own buffer, 3. sum in rank order, residual update
   for (int i = threadIdx.x * 4; i < n; i += COMM_THREADS * 4) {
     const float4 mine = *reinterpret_cast<const float4 *>(partial + i);
-    uint4 lo[COMM_MAX_WORLD], hi[COMM_MAX_WORLD];
-    unsigned pending = ((1u << c.world) - 1u) & ~(1u << c.rank);
-    unsigned polls = 0;
-    while (pending) {
-#pragma unroll
-      for (int p = 0; p < COMM_MAX_WORLD; ++p)
-        if ((pending >> p) & 1u) {
-          const uint2 *src = c.slots[c.rank] + ((size_t)buf * c.world + p) * c.n_max + i;
-          asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(lo[p].x), "=r"(lo[p].y), "=r"(lo[p].z), "=r"(lo[p].w) : "l"(src) : "memory");
-          asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(hi[p].x), "=r"(hi[p].y), "=r"(hi[p].z), "=r"(hi[p].w) : "l"(src + 2) : "memory");
-        }
-#pragma unroll
-      for (int p = 0; p < COMM_MAX_WORLD; ++p)
-        if (((pending >> p) & 1u) && (lo[p].y == tag) & (lo[p].w == tag) & (hi[p].y == tag) & (hi[p].w == tag)) pending &= ~(1u << p);
-      if (pending && (failed || ++polls >= c.wait_polls)) {
-        if (!failed) atomicExch(c.status, 100 + (__ffs(pending) - 1));  // site 100 + first peer that never arrived
-        failed = true;                                                  // give up on everything still missing
-        break;
-      }
-    }
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int p = 0; p < COMM_MAX_WORLD; ++p)
-      if (p < c.world) {
-        float4 v = mine;
-        if (p != c.rank) v = make_float4(__uint_as_float(lo[p].x), __uint_as_float(lo[p].z), __uint_as_float(hi[p].x), __uint_as_float(hi[p].z));
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    for (int p = 0; p < c.world; ++p) {
+      float4 v = mine;
+      if (p != c.rank) {
+        const uint2 *src = c.slots[c.rank] + ((size_t)buf * c.world + p) * c.n_max + i;
+        uint4 lo, hi;
+        unsigned polls = 0;
+        for (;;) {
+          asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w) : "l"(src) : "memory");
+          asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(src + 2) : "memory");
+          if ((lo.y == tag) & (lo.w == tag) & (hi.y == tag) & (hi.w == tag)) break;
+          if (failed || ++polls >= c.wait_polls) {
+            if (!failed) atomicExch(c.status, 100 + p);  // site 100 + peer that never arrived
+            failed = true;                               // give up on everything still missing
+            break;
+          }
+        }
+        v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
       }
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
     float4 r = *reinterpret_cast<float4 *>(x + i);
     r.x += __half2float(__float2half_rn(s.x));
     r.y += __half2float(__float2half_rn(s.y));
