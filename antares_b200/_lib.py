@@ -48,8 +48,10 @@ SIGNATURES = {
     "ab200_attention_prefill": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],
     "ab200_silu_mul_rows": [_vp, _vp, _i, _i, _vp],
     "ab200_residual_add_f16": [_vp, _vp, _sz, _vp],
-    "ab200_greedy_next_tp_emulated": [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp],
-    "ab200_greedy_next_tp": [_vp, _i, _i, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp],
+    "ab200_greedy_next_tp_emulated": [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp],
+    "ab200_greedy_next_tp": [_vp, _i, _i, _vp, _i, _i, _i, _vp, _i, _vp, _vp, _vp, _i, _vp],
+    "ab200_w4a16_gemv_tiled_allreduce": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _vp],
+    "ab200_w4a16_gemv_tiled_allreduce_emulated": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp],
     "ab200_w4a16_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_sigmoid": [_vp, _vp, _sz, _i, _vp],
     "ab200_rmsnorm_vsum": [_vp, _vp, _vp, _vp, _sz, _f, _f, _i, _vp],
@@ -62,10 +64,15 @@ SIGNATURES = {
     "ab200_attention_fused": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp],
     "ab200_silu_mul": [_vp, _vp, _i, _vp],
     "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
-    "ab200_greedy_next": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp],
+    "ab200_inject": [ctypes.c_char_p, _vp],
+    "ab200_forward": [_i, _vp, _i, _vp],
+    "ab200_module_info": [_i, _vp, _vp, _vp, _i],
+    "ab200_module_tensor": [_i, _i, _vp, _i, _vp, _i, _vp, _vp],
+    "ab200_forward_host_ns": [_i, _vp, _i, _vp, _i, _vp],
+    "ab200_greedy_next": [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp],
 }
 OTHER_SYMBOLS = ["ab200_last_error", "ab200_abi_version", "ab200_w4a16_gemv_workspace_bytes", "ab200_comm_buffer_bytes",
-                 "ab200_comm_emulation_scratch_bytes"]
+                 "ab200_comm_emulation_scratch_bytes", "ab200_w4a16_gemv_emulation_scratch_bytes"]
 
 _lib = None
 
@@ -91,6 +98,8 @@ def load():
         L.ab200_comm_buffer_bytes.argtypes = [_i, _i]
         L.ab200_comm_emulation_scratch_bytes.restype = ctypes.c_size_t
         L.ab200_comm_emulation_scratch_bytes.argtypes = []
+        L.ab200_w4a16_gemv_emulation_scratch_bytes.restype = ctypes.c_size_t
+        L.ab200_w4a16_gemv_emulation_scratch_bytes.argtypes = []
         _lib = L
     return _lib
 

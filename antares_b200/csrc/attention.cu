@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   if (pos < 0 || pos >= p.max_seq) {  // out-of-range step: leave cache and output untouched (all CTAs agree)
     return;
   }
+  if (splits > 1) cluster_arrive_started();
   const int S = pos + 1;
   const int HD = p.H * ATT_D;
   const int n_local = (S - split + splits - 1) / splits;  // rows split, split+splits, ... < S
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   // un-normalised output slice, max and sum into the inbox of the CTA that finalises those dims; one
   // cluster barrier; local merge.
   const int dims_per = ATT_D / splits;
+  if (splits > 1) cluster_wait_started();  // every CTA of the head is running: its inbox may be written
   if (threadIdx.x < ATT_D + splits) {
     float mx = -CUDART_INF_F;
 #pragma unroll

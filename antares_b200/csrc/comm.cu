@@ -30,7 +30,8 @@ constexpr int COMM_THREADS = 1024;
 static unsigned g_comm_wait_polls = 1u << 24;  // polls before a wait gives up (option "comm_wait_polls"); seconds at most
 
 // Receive buffer layout (per rank, in that rank's memory), n_max (value, epoch) pairs per slot:
-//   uint2 slots[2][world][n_max];  int epoch;
+//   uint2 slots[2][world][n_max];  int epoch;  int ticket (used by the all-reduce fused into the
+//   row-parallel GEMV, w4a16_gemv_ring.cu);
 struct CommPeers {
   uint2 *slots[COMM_MAX_WORLD];  // base of each rank's receive buffer (own entry = local memory)
   int *epoch;                    // this rank's epoch counter
@@ -42,7 +43,10 @@ struct CommPeers {
 __device__ __forceinline__ void allreduce_residual_body(const CommPeers &c, float *x, const float *partial, int n) {
   const int e = *c.epoch + 1, buf = e & 1;
   const unsigned tag = (unsigned)e;
-  bool failed = false;
+  // A wait that ran out earlier stays in the status word until the host reads it: every later
+  // exchange then skips its polls at once instead of spinning to its own limit again (one dead
+  // peer must not hold the GPU for 64 limits per token).
+  bool failed = *reinterpret_cast<volatile int *>(c.status) != 0;
   for (int i = threadIdx.x * 4; i < n; i += COMM_THREADS * 4) {
     const float4 v = *reinterpret_cast<const float4 *>(partial + i);
     // 1. push (value, epoch) pairs into slot `rank` of every peer's buffer
@@ -103,7 +107,7 @@ __global__ void __launch_bounds__(COMM_THREADS) allreduce_residual_kernel(CommPe
 // greedy_next kernel.  Replaces the logits all-gather + argmax of the classifier step.
 __device__ __forceinline__ void greedy_next_tp_body(const CommPeers &c, const float *__restrict__ logits, int n, int vocab_offset,
                                                     const int32_t *__restrict__ prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,
-                                                    int32_t *out_tokens) {
+                                                    int32_t *out_tokens, int out_cap) {
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sh_fail;
@@ -155,7 +159,7 @@ __device__ __forceinline__ void greedy_next_tp_body(const CommPeers &c, const fl
       asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(best)), "r"(tag), "r"((unsigned)gi), "r"(tag) : "memory");
       const uint2 *src = c.slots[c.rank] + ((size_t)buf * c.world + lane) * c.n_max;
       uint4 w;
-      unsigned polls = 0;
+      unsigned polls = (*reinterpret_cast<volatile int *>(c.status) != 0) ? c.wait_polls - 1 : 0;  // an earlier timeout is sticky: one poll only
       for (;;) {
         asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
         if ((w.y == tag) & (w.w == tag)) break;
@@ -180,18 +184,22 @@ __device__ __forceinline__ void greedy_next_tp_body(const CommPeers &c, const fl
     int next = (pi == 0x7fffffff) ? 0 : pi;
     if (prompt != nullptr && pos + 1 < n_prompt) next = prompt[pos + 1];
     *token_dev = next;
-    if (out_tokens != nullptr) out_tokens[pos + 1] = next;
-    *pos_dev = pos + 1;
+    if (out_tokens == nullptr) {
+      *pos_dev = pos + 1;
+    } else if (pos + 1 < out_cap) {  // past the end of the token log: nothing is stored, the position stays put
+      out_tokens[pos + 1] = next;
+      *pos_dev = pos + 1;
+    }
     *c.epoch = e;
   }
 }
 
 __global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_kernel(CommPeers c, const float *__restrict__ logits, int n, int vocab_offset,
                                                                       const int32_t *__restrict__ prompt, int n_prompt, int32_t *token_dev,
-                                                                      int32_t *pos_dev, int32_t *out_tokens) {
+                                                                      int32_t *pos_dev, int32_t *out_tokens, int out_cap) {
   pdl_launch_dependents();
   pdl_wait();
-  greedy_next_tp_body(c, logits, n, vocab_offset, prompt, n_prompt, token_dev, pos_dev, out_tokens);
+  greedy_next_tp_body(c, logits, n, vocab_offset, prompt, n_prompt, token_dev, pos_dev, out_tokens, out_cap);
 }
 
 // All ranks of the greedy exchange as the blocks of one cooperative launch (single-GPU protocol check).
@@ -200,11 +208,12 @@ struct GreedyEmu {
   const float *logits[COMM_MAX_WORLD];
   int n[COMM_MAX_WORLD], offset[COMM_MAX_WORLD];
   int32_t *token[COMM_MAX_WORLD], *pos[COMM_MAX_WORLD], *out_tokens[COMM_MAX_WORLD];
+  int out_cap;
 };
 __global__ void __launch_bounds__(COMM_THREADS) greedy_next_tp_emulated_kernel(const GreedyEmu *emu, const int32_t *prompt, int n_prompt) {
   const int r = blockIdx.x;
   const CommPeers c = emu->peers[r];
-  greedy_next_tp_body(c, emu->logits[r], emu->n[r], emu->offset[r], prompt, n_prompt, emu->token[r], emu->pos[r], emu->out_tokens[r]);
+  greedy_next_tp_body(c, emu->logits[r], emu->n[r], emu->offset[r], prompt, n_prompt, emu->token[r], emu->pos[r], emu->out_tokens[r], emu->out_cap);
 }
 
 // All ranks in one launch on one GPU (rank = blockIdx.x): the protocol check for machines with
@@ -234,6 +243,7 @@ static void fill_peers(CommPeers &c, void *const *bufs, int rank, int world, int
 }
 
 void comm_set_wait_polls(unsigned v) { g_comm_wait_polls = v; }
+unsigned comm_wait_polls() { return g_comm_wait_polls; }
 
 }  // namespace ab200
 
@@ -312,12 +322,14 @@ extern "C" size_t ab200_comm_emulation_scratch_bytes(void) { return sizeof(CommE
 
 extern "C" int ab200_greedy_next_tp_emulated(const float *const *logits_host, const int *n_local_host, const int *offset_host, void *const *bufs_host,
                                              int world, int n_max, const int32_t *prompt, int n_prompt, int32_t *const *token_host,
-                                             int32_t *const *pos_host, int32_t *const *out_tokens_host, void *emu_scratch_dev, void *stream) {
+                                             int32_t *const *pos_host, int32_t *const *out_tokens_host, int out_cap, void *emu_scratch_dev,
+                                             void *stream) {
   clear_error();
   AB200_REQUIRE(logits_host && n_local_host && offset_host && bufs_host && token_host && pos_host && out_tokens_host && emu_scratch_dev,
                 "greedy_next_tp_emulated: null pointer");
   AB200_REQUIRE(world >= 1 && world <= COMM_MAX_WORLD && n_max >= 4 && n_max % 4 == 0, "greedy_next_tp_emulated: bad sizes");
   GreedyEmu emu{};
+  emu.out_cap = out_cap;
   for (int r = 0; r < world; ++r) {
     fill_peers(emu.peers[r], bufs_host, r, world, n_max);
     emu.logits[r] = logits_host[r];
@@ -337,7 +349,7 @@ extern "C" int ab200_greedy_next_tp_emulated(const float *const *logits_host, co
 
 extern "C" int ab200_greedy_next_tp(const float *logits_local_f32, int n_local, int vocab_offset, void *const *bufs_host, int rank, int world,
                                     int n_max, const int32_t *prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,
-                                    int32_t *out_tokens, void *stream) {
+                                    int32_t *out_tokens, int out_cap, void *stream) {
   clear_error();
   AB200_REQUIRE(logits_local_f32 && bufs_host && token_dev && pos_dev && n_local > 0 && vocab_offset >= 0, "greedy_next_tp: bad argument");
   AB200_REQUIRE(world >= 1 && world <= COMM_MAX_WORLD && rank >= 0 && rank < world, "greedy_next_tp: rank %d / world %d", rank, world);
@@ -345,6 +357,6 @@ extern "C" int ab200_greedy_next_tp(const float *logits_local_f32, int n_local, 
   CommPeers c{};
   fill_peers(c, bufs_host, rank, world, n_max);
   AB200_CUDA(launch_pdl(greedy_next_tp_kernel, dim3(1), dim3(COMM_THREADS), 0, (cudaStream_t)stream, c, logits_local_f32, n_local, vocab_offset,
-                        prompt, n_prompt, token_dev, pos_dev, out_tokens));
+                        prompt, n_prompt, token_dev, pos_dev, out_tokens, out_cap));
   return AB200_OK;
 }

@@ -42,6 +42,7 @@ int *kernel_error_ptr();  // device address of the status word that ab200_kernel
 // overlaps the tail of the kernel before it; every kernel executes griddepcontrol.wait before
 // touching data an earlier kernel produced.
 void comm_set_wait_polls(unsigned polls);
+unsigned comm_wait_polls();
 bool pdl_enabled();
 int pdl_mode();
 void pdl_set(int mode);
@@ -64,6 +65,13 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Split cluster barrier.  A CTA may store into a peer CTA's shared memory only once that peer is
+// known to be running: every CTA arrives at kernel start (costs nothing on the streaming path) and
+// waits just before its first remote store.  Both must be executed by every thread of every CTA of
+// the cluster, convergently.
+__device__ __forceinline__ void cluster_arrive_started() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_started() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // ---- device helpers ---------------------------------------------------------------------
 

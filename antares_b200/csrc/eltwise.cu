@@ -277,7 +277,8 @@ __global__ void residual_add_f16_kernel(float *__restrict__ x, const __half *__r
 
 // Greedy token choice and loop bookkeeping in one CTA (first maximum wins, like torch.argmax).
 __global__ void __launch_bounds__(1024) greedy_next_kernel(const float *__restrict__ logits, int n, const int32_t *__restrict__ prompt,
-                                                          int n_prompt, int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens) {
+                                                          int n_prompt, int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens,
+                                                          int out_cap) {
   __shared__ float sv[32];
   __shared__ int si[32];
   float best = -CUDART_INF_F;
@@ -329,8 +330,14 @@ __global__ void __launch_bounds__(1024) greedy_next_kernel(const float *__restri
       int next = (bi == 0x7fffffff) ? 0 : bi;
       if (prompt != nullptr && pos + 1 < n_prompt) next = prompt[pos + 1];
       *token_dev = next;
-      if (out_tokens != nullptr) out_tokens[pos + 1] = next;
-      *pos_dev = pos + 1;
+      // the token log holds out_cap ids: past its end nothing is stored and the position stays put,
+      // so a step too many cannot write outside the buffer (the host counts steps and raises first)
+      if (out_tokens == nullptr) {
+        *pos_dev = pos + 1;
+      } else if (pos + 1 < out_cap) {
+        out_tokens[pos + 1] = next;
+        *pos_dev = pos + 1;
+      }
     }
   }
 }
@@ -453,10 +460,11 @@ extern "C" int ab200_rope_kv_store(const void *vqk_f16, const float *inv_freq, c
 }
 
 extern "C" int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt, int32_t *token_dev,
-                                 int32_t *pos_dev, int32_t *out_tokens, void *stream) {
+                                 int32_t *pos_dev, int32_t *out_tokens, int out_cap, void *stream) {
   clear_error();
   AB200_REQUIRE(logits_f32 && token_dev && pos_dev && n > 0, "greedy_next: bad argument");
-  greedy_next_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(logits_f32, n, prompt, n_prompt, token_dev, pos_dev, out_tokens);
+  AB200_REQUIRE(out_tokens == nullptr || out_cap > 0, "greedy_next: the token log needs a positive capacity");
+  greedy_next_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(logits_f32, n, prompt, n_prompt, token_dev, pos_dev, out_tokens, out_cap);
   AB200_CHECK_LAUNCH("greedy_next");
   return AB200_OK;
 }

@@ -104,7 +104,9 @@ __device__ __forceinline__ void unpack_pair_raw(uint32_t w0, uint32_t w1, uint32
 // the CTA that owns the column (rank r owns columns [r * 128/cs, (r+1) * 128/cs)); one cluster
 // barrier later each owner adds the cs entries of its inbox in rank order and writes the result.
 // Remote stores do not wait for a round trip and nothing reads a peer's memory after the
-// barrier, so no second barrier is needed before exit.
+// barrier, so no second barrier is needed before exit.  The caller's kernel must have executed
+// cluster_arrive_started() at its top (when the cluster has more than one CTA): the matching wait
+// here proves that every peer CTA is running before its shared memory is written.
 template <int M, int EPI, int NTHREADS, int NWARPS>
 __device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red, float *part, void *out, int N, int tile_n0) {
   namespace cg = cooperative_groups;
@@ -118,6 +120,7 @@ __device__ __forceinline__ void reduce_and_store(float (&facc)[M][4], float *red
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
   const int cols_per = TILE_N / cs;  // cs in {1,2,4,8}
+  if (cs > 1) cluster_wait_started();
   for (int i = threadIdx.x; i < M * TILE_N; i += NTHREADS) {
     const int m = i / TILE_N, c = i % TILE_N;
     float s = 0.f;
@@ -166,5 +169,13 @@ bool gemv_persist_fits(int M, int K, int N);
 int gemv_persist_dispatch(const void *x, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
                           int K, int N, int group, int pro, int epi, void *scratch, cudaStream_t s);
 int gemv_tuning_cluster();
+
+// bulk-copy ring variant (w4a16_gemv_ring.cu): batch 1, group 128, N % 128 == 0; `tiled` selects the
+// tile-major weight layout (linear bulk copies) or the reference layout (tensor-map copies)
+bool gemv_ring_eligible(int M, int K, int N, int group, bool tiled);
+int gemv_ring_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int K, int N,
+                       int epi, bool tiled, cudaStream_t s, void *const *comm_bufs = nullptr, int rank = 0, int world = 1, int n_max = 0);
+int gemv_ring_set_depth(int d);
+int gemv_ring_set_debug(int d);
 
 }  // namespace ab200

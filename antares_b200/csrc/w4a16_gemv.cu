@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f16_kernel(GemvParams
     else sp = scol + (size_t)((u_load * UNIT_K) / p.group) * ld_s;
   };
 
+  if (cs > 1) cluster_arrive_started();
   if (!p.pdl_late) pdl_launch_dependents();
   // the first NBUF units of this warp are on their way before x is staged
 #pragma unroll
@@ -430,6 +431,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) w4a16_gemv_f32_kernel(GemvParams
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned cs = cluster.num_blocks(), krank = cluster.block_rank();
+  if (cs > 1) cluster_arrive_started();
   const int tile = blockIdx.x / cs;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = tile * TILE_N + lane * 4;
@@ -624,6 +626,8 @@ static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps
     }
     return gemv_persist_dispatch(x, norm_w, eps, qw, scales, out, M, K, N, group, pro, epi, scratch, s);
   }
+  if (impl == 5 && gemv_ring_eligible(M, K, N, group, false))
+    return gemv_ring_dispatch(x, pro, norm_w, eps, qw, scales, out, K, N, epi, false, s);
   if (impl == 4 || (impl == 0 && M >= 2)) {
     bool handled = false;
     const int rc = gemv_tma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
@@ -731,6 +735,12 @@ extern "C" int ab200_w4a16_gemv_tiled(const void *x, int prologue, const void *n
   AB200_REQUIRE(prologue != PRO_RMSNORM || norm_weight_f16 != nullptr, "w4a16_gemv_tiled: RMSNorm prologue needs a weight vector");
   AB200_REQUIRE(N % TILE_N == 0, "w4a16_gemv_tiled: N=%d must be a multiple of %d for the tile-major layout", N, TILE_N);
   AB200_REQUIRE(M <= 4, "w4a16_gemv_tiled: batch %d (the tile-major path serves batches of 1-4 rows)", M);
+  {
+    const int impl = gemv_tuning_impl();
+    if ((impl == 0 || impl == 5) && gemv_ring_eligible(M, K, N, group, true))
+      return gemv_ring_dispatch(x, prologue, reinterpret_cast<const __half *>(norm_weight_f16), eps, qweight_tiled, scales_tiled, out, K, N,
+                                epilogue, true, (cudaStream_t)stream);
+  }
   GemvParams p{x, qweight_tiled, scales_tiled, out, K, N, group, K / UNIT_K, 0};
   p.norm_w = reinterpret_cast<const __half *>(norm_weight_f16);
   p.eps = eps;

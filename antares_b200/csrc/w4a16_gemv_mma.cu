@@ -460,8 +460,13 @@ int gemv_tuning_set(const char *name, int value) {
     if (value != 0 && (value < 2 || value > 4)) return fail(AB200_EINVAL, "gemv_depth must be 0 or 2..4");
     g_tune.depth = value;
   } else if (!strcmp(name, "gemv_impl")) {
-    if (value < 0 || value > 4) return fail(AB200_EINVAL, "gemv_impl must be 0 (auto), 1 (scalar pipes), 2 (cluster warp MMA), 3 (persistent warp MMA) or 4 (TMA ring)");
+    if (value < 0 || value > 5)
+      return fail(AB200_EINVAL, "gemv_impl must be 0 (auto), 1 (scalar pipes), 2 (cluster warp MMA), 3 (persistent warp MMA), 4 (TMA ring + warp MMA) or 5 (bulk-copy ring, batch 1)");
     g_tune.impl = value;
+  } else if (!strcmp(name, "ring_depth")) {
+    return gemv_ring_set_depth(value);
+  } else if (!strcmp(name, "ring_debug")) {
+    return gemv_ring_set_debug(value);
   } else {
     return fail(AB200_EINVAL, "unknown option %s", name);
   }

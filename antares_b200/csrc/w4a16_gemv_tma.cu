@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x < 16) reinterpret_cast<uint4 *>(misc)[threadIdx.x] = make_uint4(0, 0, 0, 0);
+  if (cs > 1) cluster_arrive_started();
   pdl_launch_dependents();
   __syncthreads();
 
@@ -338,6 +339,7 @@ __global__ void __launch_bounds__(T_THREADS) w4a16_gemv_tma_kernel(const __grid_
 
   // ---- reduction: K halves -> owner CTA's inbox (push) -> one cluster barrier -> rank-ordered sum -> epilogue
   const int cols_per = TILE_N / cs;
+  if (cs > 1) cluster_wait_started();  // every peer CTA is running: its inbox may be written
   for (int i = threadIdx.x; i < M * TILE_N; i += T_THREADS) {
     const int m = i / TILE_N, c = i - m * TILE_N;
     const float v = red[i] + red[M * TILE_N + i];

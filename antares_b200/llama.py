@@ -43,11 +43,25 @@ class LlamaConfig:
 _V, _Q, _K, _O, _GATE, _UP, _DOWN, _NORM = range(8)
 
 
-def synth_layer(cfg, layer):
-    """Unsharded synthetic weights of one layer (numpy)."""
+def synth_layer(cfg, layer, centered=False):
+    """Unsharded synthetic weights of one layer (numpy).  centered: zero-mean nibbles (packing.synth_w4)."""
     d, f, g = cfg.dim, cfg.ffn, cfg.group
     s = 1000 * layer
     w = {}
+    if centered:
+        import functools
+        synth = functools.partial(packing.synth_w4, centered=True)
+        parts = [synth(d, d, s + i, g) for i in (_V, _Q, _K)]
+        w["vqk_q"] = np.ascontiguousarray(np.concatenate([p[0] for p in parts], axis=1))
+        w["vqk_s"] = np.ascontiguousarray(np.concatenate([p[1] for p in parts], axis=1))
+        w["o_q"], w["o_s"] = synth(d, d, s + _O, g)
+        w["gate_q"], w["gate_s"] = synth(d, f, s + _GATE, g)
+        w["up_q"], w["up_s"] = synth(d, f, s + _UP, g)
+        w["down_q"], w["down_s"] = synth(f, d, s + _DOWN, g)
+        rng = np.random.default_rng(s + _NORM)
+        w["att_norm"] = (1 + 0.1 * rng.standard_normal(d, dtype=np.float32)).astype(np.float16)
+        w["ffn_norm"] = (1 + 0.1 * rng.standard_normal(d, dtype=np.float32)).astype(np.float16)
+        return w
     parts = [packing.synth_w4(d, d, s + i, g) for i in (_V, _Q, _K)]
     w["vqk_q"] = np.ascontiguousarray(np.concatenate([p[0] for p in parts], axis=1))  # order V, Q, K (line 27)
     w["vqk_s"] = np.ascontiguousarray(np.concatenate([p[1] for p in parts], axis=1))
@@ -105,6 +119,20 @@ def shard_layer(cfg, w, rank, world):
     return out
 
 
+class SynthWeights:
+    """Weight source for LlamaInt4Decoder(weights=...) / the oracle: the seeded synthetic model, optionally
+    with zero-mean nibbles (whose greedy stream does not settle on one token)."""
+
+    def __init__(self, cfg, centered=False):
+        self.cfg, self.centered = cfg, bool(centered)
+
+    def layer(self, l):
+        return synth_layer(self.cfg, l, self.centered)
+
+    def globals(self):
+        return synth_globals(self.cfg)
+
+
 class LlamaInt4Decoder:
     """Greedy decoder for one rank of a tensor-parallel group (world=1: the whole model).
 
@@ -113,7 +141,8 @@ class LlamaInt4Decoder:
     `weights` selects the checkpoint (gptq.GptqLlamaWeights); None = seeded synthetic weights.
     """
 
-    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None, tiled=True):
+    def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None, tiled=True,
+                 fused_allreduce=True):
         assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
         self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         self.hl = cfg.n_heads // world            # local heads
@@ -159,7 +188,9 @@ class LlamaInt4Decoder:
         self.graph = None
         self._ref_cache = {}
         self.tiled = bool(tiled)
+        self.fused_allreduce = bool(fused_allreduce)  # tensor parallel: sum over ranks inside the O / down projection kernels
         self.launches_per_step = 0
+        self._steps_left = 0   # host count of steps the cache and the token log still have room for
         self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
         self._plist = []
         for w in self.layers:
@@ -191,6 +222,9 @@ class LlamaInt4Decoder:
         """Row-parallel projection + residual: fused when alone, all-reduce of fp32 partials otherwise."""
         if self.world == 1:
             self._proj(x, q, s, self.x, prologue, 1)
+        elif self.fused_allreduce and self.tiled and hasattr(self.comm, "gemv_all_reduce_residual_"):
+            self.comm.gemv_all_reduce_residual_(self.x, x, q, s, prologue)  # projection + sum over ranks + residual: one kernel
+            self._n += 1
         elif hasattr(self.comm, "all_reduce_residual_"):
             self._proj(x, q, s, self.partial, prologue, 2)
             self.comm.all_reduce_residual_(self.x, self.partial)   # push all-reduce + residual in one kernel
@@ -229,7 +263,7 @@ class LlamaInt4Decoder:
             if self.world > 1:
                 self.comm.all_gather_into(self.logits, self.logits_local)
             call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), self._n_prompt_capture,
-                 self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), st)
+                 self.token.data_ptr(), self.pos.data_ptr(), self.out_tokens.data_ptr(), self.out_tokens.numel(), st)
         self._n += 1
         self.launches_per_step = self._n
 
@@ -291,7 +325,8 @@ class LlamaInt4Decoder:
         call("ab200_rmsnorm", self.x.data_ptr(), 1, self.final_norm.data_ptr(), self.xb.data_ptr(), 1, d, cfg.eps, st)
         call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), d, self.vl, st)
         call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), T, self.token.data_ptr(), self.pos.data_ptr(),
-             self.out_tokens.data_ptr(), st)
+             self.out_tokens.data_ptr(), self.out_tokens.numel(), st)
+        self._steps_left = min(cfg.max_seq, self.max_tokens) - T
         self.out_tokens[:T].copy_(toks)
         return int(self.token.item())
 
@@ -324,6 +359,7 @@ class LlamaInt4Decoder:
         self.pos.zero_()
         self.out_tokens.zero_()
         self.out_tokens[:1].copy_(self.prompt[:1])
+        self._steps_left = min(self.cfg.max_seq, self.max_tokens)
 
     def generate(self, prompt, n_new, batched_prefill=False):
         """Generates n_new tokens greedily after the prompt.  By default the prompt is fed token by
@@ -349,7 +385,14 @@ class LlamaInt4Decoder:
 
     def step(self, token):
         """Public per-token call with HOST token ids: copies the id in, runs one step, copies the
-        chosen id out.  Position advances on the device."""
+        chosen id out.  Position advances on the device; the host counts the steps taken since
+        reset() / prefill() and raises once the KV cache (max_seq rows) or the token log
+        (max_tokens + 1 ids) is full, instead of stepping past them."""
+        if self.graph is None:
+            raise RuntimeError("step(): call capture() first")
+        if self._steps_left <= 0:
+            raise IndexError("step(): the sequence has reached max_seq=%d / max_tokens=%d; reset() first" % (self.cfg.max_seq, self.max_tokens))
+        self._steps_left -= 1
         self._pin_in[0] = int(token)
         self.token.copy_(self._pin_in, non_blocking=True)
         self.graph.replay()

@@ -98,7 +98,7 @@ class PushComm(TorchComm):
         from ._lib import call
         call("ab200_greedy_next_tp", logits_local.data_ptr(), logits_local.numel(), int(vocab_offset),
              ctypes.cast(self._bufs_g, ctypes.c_void_p), self.rank, self.world, 4, prompt.data_ptr(), int(n_prompt),
-             token.data_ptr(), pos.data_ptr(), out_tokens.data_ptr(), torch.cuda.current_stream().cuda_stream)
+             token.data_ptr(), pos.data_ptr(), out_tokens.data_ptr(), out_tokens.numel(), torch.cuda.current_stream().cuda_stream)
 
     def all_reduce_residual_(self, x_f32, partial_f32):
         """x += fp16_round(sum over ranks of partial): one kernel, no NCCL."""
@@ -106,6 +106,17 @@ class PushComm(TorchComm):
         from ._lib import call
         call("ab200_allreduce_residual", x_f32.data_ptr(), partial_f32.data_ptr(), x_f32.numel(),
              ctypes.cast(self._bufs, ctypes.c_void_p), self.rank, self.world, self.n_max, torch.cuda.current_stream().cuda_stream)
+        return x_f32
+
+    def gemv_all_reduce_residual_(self, x_f32, act, qweight_tiled, scales_tiled, prologue):
+        """x += fp16_round(sum over ranks of act . W_rank): the row-parallel projection with the sum over
+        ranks fused into its epilogue (one kernel per rank, no separate exchange kernel)."""
+        import ctypes
+        from ._lib import call
+        K, N = qweight_tiled.shape[1] * 8, qweight_tiled.shape[0] * qweight_tiled.shape[2]
+        call("ab200_w4a16_gemv_tiled_allreduce", act.data_ptr(), int(prologue), qweight_tiled.data_ptr(), scales_tiled.data_ptr(),
+             x_f32.data_ptr(), K, N, 128, ctypes.cast(self._bufs, ctypes.c_void_p), self.rank, self.world, self.n_max,
+             torch.cuda.current_stream().cuda_stream)
         return x_f32
 
     def close(self):

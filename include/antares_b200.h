@@ -48,8 +48,10 @@ int ab200_kernel_status(int *status_host);
 
 /* Tuning knobs, the counterpart of the `config=` hints of autort.export
  * (samples/05_llama2_7b_int4.py:139).  Names: "gemv_cluster" (0 = auto, 1/2/4/8 K-slices per
- * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA),
- * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel).
+ * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA,
+ * 4 TMA ring + warp-MMA, 5 bulk-copy ring for batch 1),
+ * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel),
+ * "ring_depth" (0 auto, even 2..16: 8 KiB stages per CTA in the bulk-copy ring kernel).
  * "comm_wait_polls": polls after which the push all-reduce gives up waiting for a peer.
  * "pdl" (0 off, 1 default, 2): launch kernels with programmatic dependent launch so that a
  * kernel's weight prefetch overlaps the tail of its predecessor in the stream; every such kernel
@@ -228,9 +230,11 @@ int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *logits_f32, in
 /* Greedy sampling and loop bookkeeping on the device (lines 197-207): next = argmax(logits)
  * (first maximum) unless *pos_dev + 1 < n_prompt, in which case next = prompt[*pos_dev + 1];
  * writes next to *token_dev and to out_tokens[*pos_dev + 1] (if non-null); *pos_dev += 1.
- * For tensor-parallel vocab shards use vocab_offset and a later ab200_argmax_merge. */
+ * out_tokens holds out_cap ids: once *pos_dev + 1 reaches out_cap nothing is stored and the
+ * position no longer advances (a step too many cannot write past the log).
+ * Tensor-parallel vocabulary shards: ab200_greedy_next_tp. */
 int ab200_greedy_next(const float *logits_f32, int n, const int32_t *prompt, int n_prompt,
-                      int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, void *stream);
+                      int32_t *token_dev, int32_t *pos_dev, int32_t *out_tokens, int out_cap, void *stream);
 
 /* Generic element-wise operator: interprets a stack program compiled from an Antares-IR statement
  * `out[axes] = expr` whose tensors are all indexed by the output's axes (antares_b200/ir.py::
@@ -295,9 +299,40 @@ int ab200_comm_free(void *buf);
  * ranks, summation in rank order (bit-identical on all ranks).  bufs_host[r] = rank r's buffer as
  * mapped in this process (own entry = the local allocation).  Replaces
  * `all_reduce(partial); x = x + partial` after the row-parallel projections.  A wait that runs out
- * (a peer never arrived) is reported by ab200_kernel_status as site 100 + peer. */
+ * (a peer never arrived) is reported by ab200_kernel_status as site 100 + peer, and is sticky: while
+ * the status word is set, later exchanges poll once instead of waiting, so read (and thereby
+ * clear) the status after a step before trusting its result. */
 int ab200_allreduce_residual(float *x_f32, const float *partial_f32, int n, void *const *bufs_host,
                              int rank, int world, int n_max, void *stream);
+
+/* The row-parallel projection of a tensor-parallel decode step with the sum over ranks fused into
+ * its epilogue, one kernel per rank:
+ *   resid_f32[N] += fp16_round( sum over ranks r of  x_r[K_r] . dequant(W_r) )
+ * x is fp16 [K] (prologue 0) or fp16 [2K] = gate | up fed as silu(gate) * up (prologue 2); weights
+ * tile-major (see ab200_w4a16_gemv_tiled), group 128, K % 128 == 0, N % 128 == 0, N <= n_max.
+ * Every thread that owns an output column stores its rank's fp32 sum as a (value, epoch) pair
+ * into slot `rank` of each peer's receive buffer (plain peer stores over NVLink), polls its own
+ * buffer for the other ranks' pairs (bounded, reported like ab200_allreduce_residual), adds in rank
+ * order (bit-identical on every rank) and updates the residual.  bufs_host as for
+ * ab200_allreduce_residual; exchanges through one buffer set must be issued in the same order on
+ * every rank.  Replaces `xb = matmul_dequat(...); all_reduce(xb); x = x + xb`
+ * (samples/05_llama2_7b_int4.py:167-168,172-173 are the single-device form; the reference has no
+ * tensor-parallel path).  world == 1 degenerates to ab200_w4a16_gemv_tiled with the residual epilogue. */
+int ab200_w4a16_gemv_tiled_allreduce(const void *x, int prologue, const int32_t *qweight_tiled,
+                                     const void *scales_tiled, float *resid_f32, int K, int N,
+                                     int group, void *const *bufs_host, int rank, int world, int n_max,
+                                     void *stream);
+/* The same kernel with all `world` ranks as consecutive CTA ranges of ONE cooperative launch on one
+ * GPU (per-rank host arrays of device pointers; K_host[r] = rank r's rows, they may differ): the
+ * protocol check for machines with fewer GPUs than ranks.  emu_scratch_dev:
+ * ab200_w4a16_gemv_emulation_scratch_bytes() bytes.  Synchronises the stream once while setting up. */
+int ab200_w4a16_gemv_tiled_allreduce_emulated(const void *const *x_host, int prologue,
+                                              const int32_t *const *qweight_tiled_host,
+                                              const void *const *scales_tiled_host,
+                                              float *const *resid_host, const int *K_host, int N,
+                                              void *const *bufs_host, int world, int n_max,
+                                              void *emu_scratch_dev, void *stream);
+size_t ab200_w4a16_gemv_emulation_scratch_bytes(void);
 
 /* Vocabulary-parallel greedy step over the same kind of exchange buffer (its own one, n_max >= 4):
  * argmax of this rank's logits shard, exchange of the per-rank (value, global index) candidates by
@@ -307,7 +342,7 @@ int ab200_allreduce_residual(float *x_f32, const float *partial_f32, int n, void
 int ab200_greedy_next_tp(const float *logits_local_f32, int n_local, int vocab_offset,
                          void *const *bufs_host, int rank, int world, int n_max,
                          const int32_t *prompt, int n_prompt, int32_t *token_dev, int32_t *pos_dev,
-                         int32_t *out_tokens, void *stream);
+                         int32_t *out_tokens, int out_cap, void *stream);
 
 /* The same protocol with all `world` ranks run as the blocks of ONE cooperative launch on one
  * GPU (x_host[r], partial_host[r], bufs_host[r] = rank r's device pointers): lets the exchange
@@ -322,8 +357,43 @@ size_t ab200_comm_emulation_scratch_bytes(void);
 int ab200_greedy_next_tp_emulated(const float *const *logits_host, const int *n_local_host,
                                   const int *offset_host, void *const *bufs_host, int world, int n_max,
                                   const int32_t *prompt, int n_prompt, int32_t *const *token_host,
-                                  int32_t *const *pos_host, int32_t *const *out_tokens_host,
+                                  int32_t *const *pos_host, int32_t *const *out_tokens_host, int out_cap,
                                   void *emu_scratch_dev, void *stream);
+
+/* ---- the reference's native plugin boundary ---------------------------------------------------
+ * frameworks/pytorch/main_ops.cc:17-54 binds two calls over kernel-source text:
+ *   int  inject(const std::string &source)            -> key
+ *   void forward(int key, std::vector<Tensor> tensors)   tensors = inputs (sorted by name) ++ outputs
+ * and graph_evaluator/execute_module.hpp:274-283 reads the text's header.  The same pair here: */
+
+/* Accepts kernel-source text in the reference's wire format
+ *   // GLOBALS: name:dtype[d0, d1], ... -> name:dtype[...]        (antares/antares_compiler.py:183-199)
+ *   // BACKEND: c-b200 (device)
+ *   // COMPUTE_V1: - einstein_v2(input_dict={...}, extra_outputs=[...], exprss="<Antares IR>")
+ * (statements of the IR separated by ';', frameworks/pytorch/custom_op.py:20-32), recognises the
+ * operator natively and binds it to its hand-written kernel: W4A16 dequantise-and-multiply
+ * (samples/05_llama2_7b_int4.py:136-138; 16 rows or fewer run the decode kernel, more the tensor-core
+ * kernel), sigmoid (README.md:66 and AntaresIR.md:241), row softmax (AntaresIR.md:226).  Any other IR,
+ * or another backend name, is AB200_EUNSUPPORTED: nothing is compiled and nothing falls back.
+ * Host call, thread-safe; keys stay valid for the life of the process. */
+int ab200_inject(const char *source, int *key_out);
+
+/* Launches the module on `stream`.  args_host[i] = device pointer of the i-th tensor of the GLOBALS
+ * line, inputs first, then outputs (main_ops.cc:38-42).  Shapes are the ones the text declared.
+ * Nothing is allocated, looked up by name or synchronised on this path. */
+int ab200_forward(int key, void *const *args_host, int n_args, void *stream);
+
+/* What a binding needs to allocate outputs (custom_op.py:81-116 parses the same from the text):
+ * counts and the exported op's name, then name, dtype, shape (at most 8 extents) per argument slot. */
+int ab200_module_info(int key, int *n_inputs_host, int *n_outputs_host, char *op_name_host, int op_name_cap);
+int ab200_module_tensor(int key, int slot, char *name_host, int name_cap, char *dtype_host, int dtype_cap,
+                        long *shape8_host, int *rank_host);
+
+/* Host cost of the call path: `iters` ab200_forward calls back to back on `stream`, wall time per
+ * call in nanoseconds (the reference's per-call cost is the map rebuilding of
+ * graph_evaluator/execute_module.hpp:322-333 plus cuLaunchKernel).  Synchronises nothing. */
+int ab200_forward_host_ns(int key, void *const *args_host, int n_args, void *stream, int iters,
+                          double *ns_per_call_host);
 
 #ifdef __cplusplus
 }

@@ -12,10 +12,12 @@ from . import cport
 
 
 class OracleLlama:
-    def __init__(self, cfg):
+    def __init__(self, cfg, weights=None):
         self.cfg = cfg
-        self.layers = [L.synth_layer(cfg, l) for l in range(cfg.n_layers)]
-        self.g = L.synth_globals(cfg)
+        if weights is None:
+            weights = L.SynthWeights(cfg)
+        self.layers = [weights.layer(l) for l in range(cfg.n_layers)]
+        self.g = weights.globals()
         self.inv_freq = L.make_inv_freq(cfg.head_dim, cfg.rope_base)
         self.kc = np.zeros((cfg.n_layers, cfg.max_seq, cfg.dim), np.float16)
         self.vc = np.zeros((cfg.n_layers, cfg.max_seq, cfg.dim), np.float16)

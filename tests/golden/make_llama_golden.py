@@ -1,11 +1,20 @@
-"""Generates tests/golden/llama_tokens.json with the CPU oracle (oracle/llama_oracle.py):
-greedy token ids of the full 32-layer Llama-2-7B-architecture int4 model on seeded synthetic
-weights, for (a) an 8-token prompt + 32 generated tokens and (b) the benchmark workload's
-128-token prompt + its first 32 generated tokens.  Also records the smallest gap between the best
-and second-best logit over the generated steps: a GPU run can only be expected to reproduce the
-ids when that gap is well above the numerical tolerance.
+"""Generates tests/golden/llama_tokens.json and tests/golden/llama_logits.npz with the CPU oracle
+(oracle/llama_oracle.py): greedy token ids of the full 32-layer Llama-2-7B-architecture int4 model
+on seeded synthetic weights.
 
-  python tests/golden/make_llama_golden.py        (about 5 minutes on 8 cores)
+  p8_n32            8-token prompt + 32 generated tokens, the benchmark's weight distribution
+                    (nibbles uniform 0..15).  Its greedy stream settles on one token after a few
+                    steps (the layers add a common offset because mean(q - 8) = -0.5).
+  p128_n32          the benchmark workload: 128-token prompt + its first 32 generated tokens, same
+                    weights; full 32000-entry logits at positions 7, 127 and 158.
+  p8_n32_centered   8-token prompt + 32 generated tokens on zero-mean nibbles (every 0 replaced by 8, test-only
+                    weights): the stream does not settle (>= 20 distinct ids are required here),
+                    so token equality exercises attention, the cache and position handling on
+                    generated steps; full logits at positions 7, 20 and 38.
+For every step the smallest gap between the best and second-best logit is recorded: a GPU run
+can only be expected to reproduce an id when that gap is well above the numerical tolerance.
+
+  python tests/golden/make_llama_golden.py        (about 8 minutes on 8 cores)
 """
 import json
 import os
@@ -16,11 +25,11 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-from antares_b200.llama import LlamaConfig, synth_prompt  # noqa: E402
+from antares_b200.llama import LlamaConfig, SynthWeights, synth_prompt  # noqa: E402
 from oracle.llama_oracle import OracleLlama  # noqa: E402
 
 
-def run(model, n_prompt, n_new, seed):
+def run(model, n_prompt, n_new, seed, keep_positions, store, tag):
     prompt = synth_prompt(model.cfg, n_prompt, seed)
     model.kc[:] = 0
     model.vc[:] = 0
@@ -29,22 +38,34 @@ def run(model, n_prompt, n_new, seed):
     for lg in logits[n_prompt - 1:]:
         s = np.partition(lg, -2)[-2:]
         gaps.append(float(s[1] - s[0]))
+    for p in keep_positions:
+        store["%s_pos%d" % (tag, p)] = logits[p].astype(np.float32)
     last = logits[-1]
     return dict(n_prompt=n_prompt, n_new=n_new, prompt_seed=seed, tokens=[int(t) for t in tokens],
-                min_top2_gap=min(gaps), logit_std=float(last.std()),
+                min_top2_gap=min(gaps), top2_gaps=gaps, logit_abs_max=[float(np.abs(lg).max()) for lg in logits[n_prompt - 1:]],
+                logit_std=float(last.std()), logits_at=[int(p) for p in keep_positions],
                 last_logits_head=[float(v) for v in last[:16]], last_logits_max=float(last.max()))
 
 
 def main():
+    here = os.path.dirname(os.path.abspath(__file__))
     cfg = LlamaConfig()
-    model = OracleLlama(cfg)
+    store = {}
     out = {"config": "32 layers, d=4096, 32 heads, ffn 11008, vocab 32000, g=128, eps 1e-6, seeds per antares_b200.llama"}
-    out["p8_n32"] = run(model, 8, 32, 0)
+    model = OracleLlama(cfg, SynthWeights(cfg, centered=True))
+    out["p8_n32_centered"] = run(model, 8, 32, 0, (7, 20, 38), store, "p8_n32_centered")
+    gen = out["p8_n32_centered"]["tokens"][8:]
+    print(gen, out["p8_n32_centered"]["min_top2_gap"], flush=True)
+    assert len(set(gen)) >= 20, "the centered stream must not settle: %d distinct ids" % len(set(gen))
+    del model
+    model = OracleLlama(cfg)
+    out["p8_n32"] = run(model, 8, 32, 0, (), store, "p8_n32")
     print(out["p8_n32"]["tokens"], out["p8_n32"]["min_top2_gap"], flush=True)
-    out["p128_n32"] = run(model, 128, 32, 0)
+    out["p128_n32"] = run(model, 128, 32, 0, (7, 127, 158), store, "p128_n32")
     print(out["p128_n32"]["tokens"][128:], out["p128_n32"]["min_top2_gap"], flush=True)
-    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "llama_tokens.json"), "w") as f:
+    with open(os.path.join(here, "llama_tokens.json"), "w") as f:
         json.dump(out, f, indent=1)
+    np.savez_compressed(os.path.join(here, "llama_logits.npz"), **store)
 
 
 if __name__ == "__main__":

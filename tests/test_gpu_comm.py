@@ -105,7 +105,7 @@ def test_emulated_vocabulary_parallel_greedy_step(cuda, world):
             shards = [torch.from_numpy(full[r * vl:(r + 1) * vl].copy()).to(cuda) for r in range(world)]
             call("ab200_greedy_next_tp_emulated", arr([t.data_ptr() for t in shards]), ctypes.cast(n_arr, P), ctypes.cast(off_arr, P),
                  arr(bufs), world, 4, prompt.data_ptr(), 2, arr([t.data_ptr() for t in tok]), arr([t.data_ptr() for t in pos]),
-                 arr([t.data_ptr() for t in outs]), scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                 arr([t.data_ptr() for t in outs]), 16, scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             expect = 6 if step == 0 else int(np.argmax(full))
             want.append(expect)
@@ -118,3 +118,124 @@ def test_emulated_vocabulary_parallel_greedy_step(cuda, world):
     finally:
         for b in bufs:
             call("ab200_comm_free", b)
+
+
+def _tiled_dev(K, N, seed, cuda):
+    from antares_b200 import packing
+    qw, sc = packing.synth_w4(K, N, seed)
+    qt, st = packing.tile_weights(qw, sc)
+    return torch.from_numpy(qt).to(cuda), torch.from_numpy(st).to(cuda)
+
+
+@pytest.mark.parametrize("world,prologue", [(2, 0), (4, 2), (8, 0)])
+def test_emulated_fused_gemv_allreduce(cuda, world, prologue):
+    """The row-parallel projection with the sum over ranks fused into its epilogue, all ranks as CTA
+    ranges of one cooperative launch: uneven K shards (22 groups over the ranks), several exchanges in a
+    row (both slot sets, the ticket that advances the epoch), every rank bit-identical, and equal to
+    the rank-ordered fp32 sum of the per-rank projections computed by the same kernel alone."""
+    from antares_b200 import packing
+    K_total, N, n_max = 2816, 512, 512
+    bounds = packing.row_shard_bounds(K_total, world)
+    Ks = [k1 - k0 for k0, k1 in bounds]
+    assert len(set(Ks)) > 1 or world == 2
+    bufs = [_alloc(world, n_max) for _ in range(world)]
+    ops.set_option("gemv_cluster", 2)  # same K split in the fused and the stand-alone launches: identical partial sums
+    try:
+        L = _lib.load()
+        scratch = torch.zeros(int(L.ab200_w4a16_gemv_emulation_scratch_bytes()), dtype=torch.uint8, device=cuda)
+        weights = [_tiled_dev(Ks[r], N, 900 + r, cuda) for r in range(world)]
+        rng = np.random.default_rng(world)
+        x0 = rng.standard_normal(N).astype(np.float32)
+        xs = [torch.from_numpy(x0.copy()).to(cuda) for _ in range(world)]
+        want = torch.from_numpy(x0.copy()).to(cuda)
+        P = ctypes.c_void_p
+        arr = lambda v: ctypes.cast((P * world)(*v), P)
+        st = torch.cuda.current_stream().cuda_stream
+        for step in range(4):
+            width = 2 if prologue == 2 else 1
+            acts = [torch.from_numpy(rng.standard_normal((1, width * Ks[r])).astype(np.float16)).to(cuda) for r in range(world)]
+            k_arr = (ctypes.c_int * world)(*Ks)
+            call("ab200_w4a16_gemv_tiled_allreduce_emulated", arr([a.data_ptr() for a in acts]), prologue,
+                 arr([w[0].data_ptr() for w in weights]), arr([w[1].data_ptr() for w in weights]), arr([x.data_ptr() for x in xs]),
+                 ctypes.cast(k_arr, P), N, arr(bufs), world, n_max, scratch.data_ptr(), st)
+            torch.cuda.synchronize()
+            total = torch.zeros(N, dtype=torch.float32, device=cuda)
+            for r in range(world):  # rank order, fp32
+                part = torch.empty((1, N), dtype=torch.float32, device=cuda)
+                ops.w4a16_gemv_tiled(acts[r], weights[r][0], weights[r][1], part, prologue=prologue, epilogue=ops.EPI_F32)
+                total = total + part[0]
+            want = want + total.to(torch.float16).to(torch.float32)
+            for r in range(world):
+                assert torch.equal(xs[r], xs[0]), "ranks must hold bit-identical results (step %d)" % step
+            assert torch.equal(xs[0], want), "step %d" % step
+        assert ops.kernel_status() == 0
+    finally:
+        ops.set_option("gemv_cluster", 0)
+        for b in bufs:
+            call("ab200_comm_free", b)
+
+
+def test_fused_gemv_allreduce_missing_peer_times_out_then_stays_fast(cuda):
+    """Rank 0 of a 2-rank group whose peer never pushes, through the fused projection: the bounded wait
+    gives up and names the peer; while the status word is set a second exchange returns without
+    waiting again (a timeout is sticky until the host reads it); afterwards the context is usable."""
+    import time
+    K, N = 512, 512
+    bufs = [_alloc(2, N), _alloc(2, N)]
+    ops.set_option("comm_wait_polls", 1 << 16)
+    try:
+        qt, st_ = _tiled_dev(K, N, 950, cuda)
+        act = torch.ones((1, K), dtype=torch.float16, device=cuda)
+        x = torch.zeros(N, device=cuda)
+        bufs_arr = (ctypes.c_void_p * 2)(*bufs)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def exchange():
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            call("ab200_w4a16_gemv_tiled_allreduce", act.data_ptr(), 0, qt.data_ptr(), st_.data_ptr(), x.data_ptr(), K, N, 128,
+                 ctypes.cast(bufs_arr, ctypes.c_void_p), 0, 2, N, stream)
+            torch.cuda.synchronize()
+            return time.perf_counter() - t0
+
+        t_first = exchange()
+        t_second = exchange()           # status still set: polls once
+        assert t_second < max(0.25 * t_first, 2e-3), (t_first, t_second)
+        with pytest.raises(_lib.Ab200Error) as ei:
+            ops.kernel_status()
+        assert ei.value.code == _lib.ETIMEOUT and "site 101" in str(ei.value)
+        assert ops.kernel_status() == 0
+        assert float((torch.ones(8, device=cuda) * 2).sum()) == 16.0
+    finally:
+        ops.set_option("comm_wait_polls", 1 << 24)
+        for b in bufs:
+            call("ab200_comm_free", b)
+
+
+def test_greedy_next_never_writes_past_the_token_log(cuda):
+    """The token log holds out_cap ids: a step too many stores nothing and leaves the position where
+    it was (single-GPU kernel and the vocabulary-parallel one)."""
+    logits = torch.zeros(100, device=cuda)
+    logits[42] = 1.0
+    tok = torch.zeros(1, dtype=torch.int32, device=cuda)
+    pos = torch.zeros(1, dtype=torch.int32, device=cuda)
+    log = torch.full((8,), -7, dtype=torch.int32, device=cuda)   # capacity 4 declared, 4 guard entries behind it
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(6):
+        call("ab200_greedy_next", logits.data_ptr(), 100, None, 0, tok.data_ptr(), pos.data_ptr(), log.data_ptr(), 4, st)
+    torch.cuda.synchronize()
+    assert log.cpu().tolist() == [-7, 42, 42, 42, -7, -7, -7, -7]
+    assert int(pos.item()) == 3 and int(tok.item()) == 42
+    bufs = [_alloc(1, 4)]
+    try:
+        pos.zero_()
+        log.fill_(-7)
+        bufs_arr = (ctypes.c_void_p * 1)(*bufs)
+        for _ in range(6):
+            call("ab200_greedy_next_tp", logits.data_ptr(), 100, 0, ctypes.cast(bufs_arr, ctypes.c_void_p), 0, 1, 4, None, 0,
+                 tok.data_ptr(), pos.data_ptr(), log.data_ptr(), 4, st)
+        torch.cuda.synchronize()
+        assert log.cpu().tolist() == [-7, 42, 42, 42, -7, -7, -7, -7]
+        assert int(pos.item()) == 3
+    finally:
+        call("ab200_comm_free", bufs[0])

@@ -309,3 +309,91 @@ def test_gemv_accuracy_on_awkward_activations(cuda, impl, kind):
         ops.set_option("gemv_impl", 0)
     assert np.isfinite(y.astype(np.float32)).all()
     assert _err(y, ref) <= TOL
+
+
+# Shapes of the decode projections at 1, 2, 4 and 8 tensor-parallel ranks (K slices of 1..86 groups,
+# uneven cluster splits) plus the smallest legal ones.
+RING_SHAPES = [(128, 128), (256, 256), (4096, 4096), (4096, 12288), (4096, 22016), (11008, 4096), (5504, 4096), (2816, 4096),
+               (1408, 4096), (1280, 4096), (512, 4096), (4096, 1536), (4096, 2816)]
+
+
+@pytest.mark.parametrize("K,N", RING_SHAPES)
+def test_bulk_ring_gemv_both_layouts(cuda, K, N):
+    """The batch-1 bulk-copy ring kernel: every prologue and epilogue against the oracle, on the
+    tile-major layout (linear bulk copies) and on the reference layout (tensor-map copies); the two
+    must agree bit for bit (same arithmetic, only the copy engine's addressing differs), and a
+    second run must repeat the first bit for bit."""
+    qw, sc = packing.synth_w4(K, N, 700 + K + N)
+    qt, st = packing.tile_weights(qw, sc)
+    rng = np.random.default_rng(701)
+    x16 = packing.synth_x(1, K, 702)
+    x32 = (rng.standard_normal((1, K)) * 3).astype(np.float32)
+    gu = rng.standard_normal((1, 2 * K)).astype(np.float16)
+    wn = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    refs = {
+        ops.PRO_PLAIN: cport.w4a16_gemm(x16, qw, sc).astype(np.float32),
+        ops.PRO_RMSNORM: cport.w4a16_gemm(cport.rmsnorm(x32, wn, 1e-6), qw, sc).astype(np.float32),
+        ops.PRO_SILU_MUL: cport.w4a16_gemm(cport.silu_mul(gu[0, :K].copy(), gu[0, K:].copy())[None, :], qw, sc).astype(np.float32),
+    }
+    ins = {ops.PRO_PLAIN: _dev(x16, cuda), ops.PRO_RMSNORM: _dev(x32, cuda), ops.PRO_SILU_MUL: _dev(gu, cuda)}
+    dq, ds, dqt, dst, dwn = _dev(qw, cuda), _dev(sc, cuda), _dev(qt, cuda), _dev(st, cuda), _dev(wn, cuda)
+    resid0 = rng.standard_normal((1, N)).astype(np.float32)
+    ops.set_option("gemv_impl", 5)
+    try:
+        for pro, ref in refs.items():
+            nw = dwn if pro == ops.PRO_RMSNORM else None
+            for epi, dt in ((ops.EPI_F16, torch.float16), (ops.EPI_RESIDUAL, torch.float32), (ops.EPI_F32, torch.float32)):
+                outs = []
+                for rep in range(2):
+                    a = _dev(resid0, cuda).to(dt)
+                    b = a.clone()
+                    ops.w4a16_gemv_tiled(ins[pro], dqt, dst, a, prologue=pro, epilogue=epi, norm_weight=nw)
+                    ops.w4a16_gemv_fused(ins[pro], dq, ds, b, prologue=pro, epilogue=epi, norm_weight=nw)
+                    assert torch.equal(a, b), (pro, epi)
+                    outs.append(a)
+                assert torch.equal(outs[0], outs[1]), "results must be bitwise repeatable"
+                want = ref + resid0 if epi == ops.EPI_RESIDUAL else ref
+                assert _err(outs[0].float().cpu().numpy(), want) <= TOL, (pro, epi)
+    finally:
+        ops.set_option("gemv_impl", 0)
+    assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("depth", [2, 4, 16])
+@pytest.mark.parametrize("cluster", [1, 2, 8])
+def test_bulk_ring_gemv_depths_and_clusters(cuda, depth, cluster):
+    """Ring depth and K split change only the schedule: wrap-around of the ring (depth below the
+    number of stages) and one-stage slices give the oracle's result."""
+    K, N = 2816, 512   # 22 stages: 22, 11 or 2-3 per CTA
+    qw, sc = packing.synth_w4(K, N, 710)
+    qt, st = packing.tile_weights(qw, sc)
+    x = packing.synth_x(1, K, 711)
+    ref = cport.w4a16_gemm(x, qw, sc)
+    y = torch.empty((1, N), dtype=torch.float16, device=cuda)
+    ops.set_option("ring_depth", depth)
+    ops.set_option("gemv_cluster", cluster)
+    try:
+        ops.w4a16_gemv_tiled(_dev(x, cuda), _dev(qt, cuda), _dev(st, cuda), y)
+    finally:
+        ops.set_option("ring_depth", 0)
+        ops.set_option("gemv_cluster", 0)
+    assert _err(y.cpu().numpy(), ref) <= TOL
+    assert ops.kernel_status() == 0
+
+
+def test_bulk_ring_gemv_accuracy_on_awkward_activations(cuda):
+    K, N = 4096, 4096
+    qw, sc = packing.synth_w4(K, N, 61)
+    qt, st = packing.tile_weights(qw, sc)
+    dqt, dst = _dev(qt, cuda), _dev(st, cuda)
+    rng = np.random.default_rng(62)
+    for kind in ("offset", "outlier", "tiny", "huge", "zero"):
+        x = rng.standard_normal((1, K))
+        x = {"offset": 10 + x, "outlier": np.where(np.arange(K) == 7, 300.0, x), "tiny": x * 1e-4, "huge": x * 2e3, "zero": x * 0}[kind]
+        x = x.astype(np.float16)
+        ref = cport.w4a16_gemm(x, qw, sc)
+        y = torch.empty((1, N), dtype=torch.float16, device=cuda)
+        ops.w4a16_gemv_tiled(_dev(x, cuda), dqt, dst, y)
+        y = y.cpu().numpy()
+        assert np.isfinite(y.astype(np.float32)).all(), kind
+        assert np.abs(y.astype(np.float32) - ref.astype(np.float32)).max() <= TOL * max(np.abs(ref.astype(np.float32)).max(), 1e-30), kind
