@@ -24,6 +24,14 @@ from . import ops as _ops
 
 RMS_EPS = 1e-6  # epsilon of the built-in rmsnorm ops (the reference's value is inside its closed wheel)
 
+# The W4A16 program of the reference's int4 sample (samples/05_llama2_7b_int4.py:136-138), for callers that
+# want the exported op without retyping the IR.
+W4A16_IR_SAMPLE = """
+  input1[S, N] = (qweight[S / 8, N] >> (S % 8 * 4)).call(strs.bitwise_and, 15) * input0[S].like(1)
+  w[S, N] = scales[S / 128, N] * (input1[S, N] - 8)
+  my_result[N] +=! input0[S] * w[S, N].to(input0.dtype())
+"""
+
 _TORCH_DT = {"float16": torch.float16, "float32": torch.float32, "int32": torch.int32}
 
 
@@ -66,25 +74,70 @@ def _split_call(match, tensors, out):
     return by_name, out
 
 
+class NativeModules:
+    """Keys of the library's native plugin boundary (ab200_inject / ab200_forward, the counterpart of
+    frameworks/pytorch/main_ops.cc:17-54) for one exported op: the kernel-source text is written in the
+    reference's wire format for the shapes of a call, injected once per distinct shape set, and every call
+    goes through ab200_forward with raw pointers - the same entry a C++ binding would use, so there is one
+    recogniser for both routes (the IR is matched natively; Python only formats the header)."""
+
+    def __init__(self, ir_text, input_specs, out_name):
+        self.ir = "; ".join(_ir.split_statements(ir_text))
+        self.specs, self.out_name = input_specs, out_name
+        self.order = sorted(range(len(input_specs)), key=lambda i: input_specs[i].name)  # inputs sorted by name (lang/generic.py:53-54)
+        self.keys = {}
+
+    def source(self, shapes, out_dtype, out_shape):
+        ins = ", ".join("%s:%s[%s]" % (self.specs[i].name, self.specs[i].dtype, ", ".join(str(d) for d in shapes[i])) for i in self.order)
+        outs = "%s:%s[%s]" % (self.out_name, out_dtype, ", ".join(str(d) for d in out_shape))
+        return ("// GLOBALS: %s -> %s\n// BACKEND: c-b200 (default)\n// CONFIG: \n// COMPUTE_V1: - einstein_v2(input_dict={}, extra_outputs=[], exprss=\"%s\")\n"
+                % (ins, outs, self.ir))
+
+    def forward(self, tensors, out, out_dtype_name):
+        import ctypes
+        from ._lib import call
+        shapes = tuple(tuple(t.shape) for t in tensors)
+        sig = (shapes, tuple(out.shape))
+        key = self.keys.get(sig)
+        if key is None:
+            k = ctypes.c_int(-1)
+            call("ab200_inject", self.source(shapes, out_dtype_name, tuple(out.shape)).encode(), ctypes.cast(ctypes.pointer(k), ctypes.c_void_p))
+            key = self.keys[sig] = k.value
+        n = len(tensors) + 1
+        args = (ctypes.c_void_p * n)(*([tensors[i].data_ptr() for i in self.order] + [out.data_ptr()]))
+        call("ab200_forward", key, ctypes.cast(args, ctypes.c_void_p), n, torch.cuda.current_stream().cuda_stream)
+        return out
+
+
+_DT_NAME = {torch.float16: "float16", torch.float32: "float32"}
+
+
 def export(ir, inputs, config=None, name=None):
     """Binds an Antares-IR program to its hand-written kernel and registers it as autort.ops.<name>."""
     match = _ir.recognise(ir, inputs, name)
-    if match.kind == "w4a16":
+    if match.kind in ("w4a16", "sigmoid", "softmax"):
         pr = match.params
+        native = NativeModules(ir, match.inputs, match.output)
 
         def fn(*tensors, out=None, extra=None):
             t, out = _split_call(match, tensors, out)
-            x, qw, sc = t[pr["x"]], t[pr["qweight"]], t[pr["scales"]]
-            res = _ops.w4a16_matmul(x, qw, sc, out=out, group=pr["group"])
-            return res
-    elif match.kind == "sigmoid":
-        def fn(*tensors, out=None, extra=None):
-            t, out = _split_call(match, tensors, out)
-            return _ops.sigmoid(t[match.params["x"]], out=out)
-    elif match.kind == "softmax":
-        def fn(*tensors, out=None, extra=None):
-            t, out = _split_call(match, tensors, out)
-            return _ops.softmax(t[match.params["x"]], out=out)
+            ordered = [t[s.name] for s in match.inputs]
+            for a in ordered:
+                if not a.is_cuda:
+                    raise ValueError("%s: tensors must live on a CUDA device (there is no CPU path)" % match.name)
+            x = t[pr["x"]]
+            if match.kind == "w4a16":
+                qw = t[pr["qweight"]]
+                shape = tuple(x.shape[:-1]) + (qw.shape[1],)
+            else:
+                shape = tuple(x.shape)
+            if out is None:
+                out = torch.empty(shape, dtype=x.dtype, device=x.device)
+            elif out.numel() != int(torch.Size(shape).numel()) or out.dtype != x.dtype or not out.is_contiguous():
+                raise ValueError("%s: out must be a contiguous %s tensor of %d elements" % (match.name, x.dtype, torch.Size(shape).numel()))
+            native.forward(ordered, out.view(shape) if out.shape != shape else out, _DT_NAME[x.dtype])
+            return out
+        fn.native = native
     elif match.kind == "eltwise":
         pr = match.params
 

@@ -67,10 +67,10 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Split cluster barrier.  A CTA may store into a peer CTA's shared memory only once that peer is
-// known to be running: every CTA arrives at kernel start (costs nothing on the streaming path) and
-// waits just before its first remote store.  Both must be executed by every thread of every CTA of
+// known to be running: every CTA arrives at kernel start (relaxed: it orders no memory, so it costs
+// nothing on the streaming path) and waits just before its first remote store.  Both must be executed by every thread of every CTA of
 // the cluster, convergently.
-__device__ __forceinline__ void cluster_arrive_started() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_started() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_started() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // ---- device helpers ---------------------------------------------------------------------

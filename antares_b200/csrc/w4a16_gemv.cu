@@ -737,7 +737,9 @@ extern "C" int ab200_w4a16_gemv_tiled(const void *x, int prologue, const void *n
   AB200_REQUIRE(M <= 4, "w4a16_gemv_tiled: batch %d (the tile-major path serves batches of 1-4 rows)", M);
   {
     const int impl = gemv_tuning_impl();
-    if ((impl == 0 || impl == 5) && gemv_ring_eligible(M, K, N, group, true))
+    // the bulk-copy ring kernel on request; in a decode step (a chain of dependent kernels) it runs level with
+    // the register-prefetch kernel, whose smaller footprint lets the next kernel's CTAs become resident earlier
+    if (impl == 5 && gemv_ring_eligible(M, K, N, group, true))
       return gemv_ring_dispatch(x, prologue, reinterpret_cast<const __half *>(norm_weight_f16), eps, qweight_tiled, scales_tiled, out, K, N,
                                 epilogue, true, (cudaStream_t)stream);
   }

@@ -17,9 +17,9 @@
 // dependent launch they stream while the predecessor is still in its tail and while this
 // kernel's activations are being staged.
 //
-// Eight consumer warps in two groups: stage s belongs to group s & 1, and warp j of the group
-// takes packed rows 4j..4j+3 (32 k) of it: four conflict-free 16-byte shared loads (lane l reads
-// columns 4l..4l+3), then the raw-nibble multiply of the scalar kernel: `w & 0x000F000F` is a pair
+// Eight consumer warps in four pairs: stage s belongs to pair s & 3, and the pair's two warps take
+// packed rows 0-7 and 8-15 of it: eight conflict-free 16-byte shared loads per thread (lane l reads
+// columns 4l..4l+3), 32 packed words per visit, then the raw-nibble multiply of the scalar kernel: `w & 0x000F000F` is a pair
 // of fp16 subnormals q * 2^-24 (`w & 0x00F000F0` = 16 q * 2^-24), multiplied on the FP16 pipe by
 // activations pre-scaled by a power of two, 16 products per half2 lane, widened to fp32, zero-point
 // removed as 8 * sum(x) per 32-k unit, times the group scale.  A warp hands its part of a stage
@@ -73,7 +73,7 @@ struct RingParams {
   int *status;
   int K, N;
   int groups;   // K / 128 = stages per column tile
-  int depth;    // ring stages (even)
+  int depth;    // ring stages (a multiple of 4)
   int tiled;    // 1: tile-major weights, linear bulk copies; 0: reference layout, tensor-map copies
   int pdl_late;
   int debug;    // investigation only: 1 consumers skip the math, 2 no copies beyond the first ring fill and no waits
@@ -101,6 +101,9 @@ __device__ __forceinline__ bool r_mbar_wait(uint32_t bar, unsigned parity, unsig
   }
   return false;
 }
+
+// Out of the streaming loop's way: entered only when the first try did not succeed.
+__device__ __noinline__ bool r_mbar_wait_slow(uint32_t bar, unsigned parity, unsigned polls) { return r_mbar_wait(bar, parity, polls); }
 
 __device__ __forceinline__ void r_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
@@ -342,7 +345,7 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
   if (threadIdx.x == 0) {
     for (int i = 0; i < D; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8 * i));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars + 8 * (D + i)), "n"(R_CWARPS / 2));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(bars + 8 * (D + i)));  // the two warps that share a stage
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_sc));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -415,64 +418,88 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
     ring_stage_x<PRO>(p, k_begin, rows, xs, corr, &sh_back, sh_f, sh_u, nw_pre, wmax_pre);
     r_consumer_sync();
 
-    const int grp = warp >> 2, j = warp & 3;
-    bool alive = true;
+    // Stage s belongs to warp pair s & 3; the pair's warps take packed rows 0-7 and 8-15 of it: 32 packed
+    // words per thread and visit, so that the per-visit bookkeeping (wait, hand-back, pointer bumps) is
+    // spread over 256 multiply-adds.  All operands come through 32-bit shared addresses.
+    const int pr = warp >> 1, hf = warp & 1;
     if (nst > 0 && !r_mbar_wait(bar_sc, 0, p.wait_polls)) {
       if (lane == 0) atomicExch(p.status, 420);  // site 420: the scale rows never arrived
-      alive = false;
     }
-    const uint4 *xp = reinterpret_cast<const uint4 *>(xs) + grp * R_STAGE_ROWS + j * 4;
-    const float *cp = corr + grp * 4 + j;
-    const unsigned char *sp = sc_s + grp * R_SCALE_ROW_BYTES + lane * 8;
-    const uint32_t w_off = (uint32_t)(j * 4 * 512 + lane * 16);
-    int slot = grp, round = 0;  // D is even: a slot keeps the parity of its stage
+    uint32_t w_addr = r_smem_u32(ring) + (uint32_t)(pr * R_STAGE_BYTES + hf * (R_STAGE_BYTES / 2) + lane * 16);
+    const uint32_t w_end = r_smem_u32(ring) + (uint32_t)(D * R_STAGE_BYTES);
+    uint32_t full_addr = bars + 8 * pr, empty_addr = bars + 8 * (D + pr);
+    uint32_t x_addr = r_smem_u32(xs) + (uint32_t)((pr * R_STAGE_ROWS + hf * 8) * 16);
+    uint32_t c_addr = r_smem_u32(corr) + (uint32_t)((pr * 4 + hf * 2) * 4);
+    uint32_t s_addr = r_smem_u32(sc_s) + (uint32_t)(pr * R_SCALE_ROW_BYTES + lane * 8);
+    unsigned parity = 0;
+    const bool free_run = (p.debug & 2) != 0;
     constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
-    for (int s = grp; s < nst; s += 2) {
-      if (alive && !((p.debug & 2) && round > 0) && !r_mbar_wait(bars + 8 * slot, round & 1, p.wait_polls)) {
-        if (lane == 0) atomicExch(p.status, 410 + slot);  // site 410: a ring stage never arrived
-        alive = false;                                    // stop waiting; the result is void
+    // The barrier of the NEXT visit is probed (test_wait: never blocks) right after this visit's words
+    // are in registers, so the probe's latency hides behind the multiply-adds; `ready` carries the
+    // answer into the next round, which only enters the waiting path when the stage was not there yet.
+    uint32_t ready = 0;
+    if (pr < nst) asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                               : "=r"(ready) : "r"(full_addr), "r"(parity) : "memory");
+    for (int s = pr; s < nst; s += 4) {
+      if (!ready && !(free_run && s >= D) && !r_mbar_wait_slow(full_addr, parity, p.wait_polls)) {
+        if (lane == 0) atomicExch(p.status, 410 + pr);  // site 410: a ring stage never arrived
+        break;                                          // stop waiting; the result is void
       }
-      const unsigned char *wsrc = ring + slot * R_STAGE_BYTES + w_off;
-      uint4 wv[4];
+      uint4 wv[8];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) wv[r] = *reinterpret_cast<const uint4 *>(wsrc + r * 512);
-      const uint2 sv = *reinterpret_cast<const uint2 *>(sp);
-      // the packed words are in registers: hand this warp's part of the stage back
+      for (int r = 0; r < 8; ++r) wv[r] = lds128(w_addr + r * 512);
+      uint2 sv, zz;
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sv.x), "=r"(sv.y) : "r"(s_addr));
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(zz.x), "=r"(zz.y) : "r"(c_addr));
+      // the packed words are in registers: hand this warp's half of the stage back
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bars + 8 * (D + slot)) : "memory");
-      __half2 hacc[4] = {u2h2(0u), u2h2(0u), u2h2(0u), u2h2(0u)};
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_addr) : "memory");
+      {  // advance to the next visit's slot and probe it
+        w_addr += 4 * R_STAGE_BYTES;
+        full_addr += 32;
+        empty_addr += 32;
+        if (w_addr >= w_end) {  // D is a multiple of 4: a slot always serves the same pair
+          w_addr -= (uint32_t)(D * R_STAGE_BYTES);
+          full_addr -= 8 * D;
+          empty_addr -= 8 * D;
+          parity ^= 1u;
+        }
+        ready = 0;
+        if (s + 4 < nst) asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                                      : "=r"(ready) : "r"(full_addr), "r"(parity) : "memory");
+      }
       if (p.debug & 1) {
-        facc[0] += __uint_as_float(wv[0].x ^ wv[1].y ^ wv[2].z ^ wv[3].w);
-      } else
+        facc[0] += __uint_as_float(wv[0].x ^ wv[1].y ^ wv[2].z ^ wv[3].w ^ wv[4].x ^ wv[5].y ^ wv[6].z ^ wv[7].w);
+      } else {
+        const float2 s01 = __half22float2(u2h2(sv.x)), s23 = __half22float2(u2h2(sv.y));
+        const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint4 xr = xp[r];
-        const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+        for (int u = 0; u < 2; ++u) {
+          __half2 hacc[4] = {u2h2(0u), u2h2(0u), u2h2(0u), u2h2(0u)};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t w = wr[c], w8 = w >> 8;
-          hacc[c] = __hfma2(u2h2(w & LO), u2h2(xr.x), hacc[c]);
-          hacc[c] = __hfma2(u2h2(w & HI), u2h2(xr.y), hacc[c]);
-          hacc[c] = __hfma2(u2h2(w8 & LO), u2h2(xr.z), hacc[c]);
-          hacc[c] = __hfma2(u2h2(w8 & HI), u2h2(xr.w), hacc[c]);
+          for (int r = 0; r < 4; ++r) {
+            const uint4 xr = lds128(x_addr + (u * 4 + r) * 16);
+            const uint32_t wr[4] = {wv[u * 4 + r].x, wv[u * 4 + r].y, wv[u * 4 + r].z, wv[u * 4 + r].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint32_t w = wr[c], w8 = w >> 8;
+              hacc[c] = __hfma2(u2h2(w & LO), u2h2(xr.x), hacc[c]);
+              hacc[c] = __hfma2(u2h2(w & HI), u2h2(xr.y), hacc[c]);
+              hacc[c] = __hfma2(u2h2(w8 & LO), u2h2(xr.z), hacc[c]);
+              hacc[c] = __hfma2(u2h2(w8 & HI), u2h2(xr.w), hacc[c]);
+            }
+          }
+          const float zp = __uint_as_float(u ? zz.y : zz.x);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float2 f = __half22float2(hacc[c]);
+            facc[c] = fmaf(sc[c], (f.x + f.y) - zp, facc[c]);
+          }
         }
       }
-      const float zp = *cp;
-      const float2 s01 = __half22float2(u2h2(sv.x)), s23 = __half22float2(u2h2(sv.y));
-      const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float2 f = __half22float2(hacc[c]);
-        facc[c] = fmaf(sc[c], (f.x + f.y) - zp, facc[c]);
-      }
-      xp += 2 * R_STAGE_ROWS;
-      cp += 8;
-      sp += 2 * R_SCALE_ROW_BYTES;
-      slot += 2;
-      if (slot >= D) {
-        slot -= D;
-        ++round;
-      }
+      x_addr += 4 * R_STAGE_ROWS * 16;
+      c_addr += 4 * 4 * 4;
+      s_addr += 4 * R_SCALE_ROW_BYTES;
     }
     if (p.pdl_late) pdl_launch_dependents();
     const float back = sh_back;
@@ -566,7 +593,7 @@ int gemv_ring_set_debug(int d) { g_ring_debug = d; return AB200_OK; }
 static unsigned g_ring_wait_polls = 1u << 22;
 
 int gemv_ring_set_depth(int d) {
-  if (d != 0 && (d < 2 || d > R_MAX_DEPTH || (d & 1))) return fail(AB200_EINVAL, "ring_depth must be 0 (auto) or an even number in 2..%d", R_MAX_DEPTH);
+  if (d != 0 && (d < 4 || d > R_MAX_DEPTH || (d & 3))) return fail(AB200_EINVAL, "ring_depth must be 0 (auto) or a multiple of 4 up to %d", R_MAX_DEPTH);
   g_ring_depth = d;
   return AB200_OK;
 }
@@ -626,14 +653,23 @@ static int ring_plan(int K, int N, RingPlan &pl) {
   }
   while (cs > 1 && groups / cs < 1) cs /= 2;
   const int nst_max = (groups + cs - 1) / cs;
-  int depth = g_ring_depth ? g_ring_depth : 6;
-  if (depth > ((nst_max + 1) & ~1)) depth = (nst_max + 1) & ~1;
-  if (depth < 2) depth = 2;
+  // ring depth: as deep as lets every CTA of the grid be resident at once (a multiple of 4 stages)
+  const size_t fixed = (size_t)nst_max * (R_SCALE_ROW_BYTES + 256 + 16) + (size_t)(R_CWARPS + 1) * TILE_N * sizeof(float);
+  int depth = g_ring_depth;
+  if (depth == 0) {
+    int per_sm = (tiles * cs + sm_count() - 1) / sm_count();
+    if (per_sm > 4) per_sm = 4;
+    const size_t budget = (size_t)225 * 1024 / per_sm - 1024;
+    depth = budget > fixed ? (int)((budget - fixed) / R_STAGE_BYTES) & ~3 : 4;
+    if (depth > 12) depth = 12;
+  }
+  if (depth > ((nst_max + 3) & ~3)) depth = (nst_max + 3) & ~3;
+  if (depth < 4) depth = 4;
   pl.tiles = tiles;
   pl.cs = cs;
   pl.depth = depth;
   pl.nst_max = nst_max;
-  pl.smem = (size_t)depth * R_STAGE_BYTES + (size_t)nst_max * (R_SCALE_ROW_BYTES + 256 + 16) + (size_t)(R_CWARPS + 1) * TILE_N * sizeof(float);
+  pl.smem = (size_t)depth * R_STAGE_BYTES + fixed;
   if (pl.smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "w4a16_gemv: K slice of %d groups does not fit shared memory", nst_max);
   return AB200_OK;
 }

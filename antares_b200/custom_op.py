@@ -41,6 +41,11 @@ class CustomOp(torch.nn.Module):
 
     def emit(self):
         self.match = _ir.recognise(self.ir, self.specs)
+        if self.match.kind in ("w4a16", "sigmoid", "softmax"):
+            # the named family goes through the native plugin boundary (ab200_inject / ab200_forward), as the
+            # reference's forward() goes through custom_lib.inject / custom_lib.forward (custom_op.py:117-148)
+            from .autort_api import NativeModules
+            self.native = NativeModules(self.ir, self.match.inputs, self.match.output)
         return self
 
     def forward(self, *inputs):
@@ -50,12 +55,12 @@ class CustomOp(torch.nn.Module):
             raise TypeError("expected %d inputs" % len(self.input_names))
         t = {k: v.contiguous().to(self.custom_device) for k, v in zip(self.input_names, inputs)}
         pr = self.match.params
-        if self.match.kind == "w4a16":
-            return _ops.w4a16_matmul(t[pr["x"]], t[pr["qweight"]], t[pr["scales"]], group=pr["group"])
-        if self.match.kind == "sigmoid":
-            return _ops.sigmoid(t[pr["x"]])
-        if self.match.kind == "softmax":
-            return _ops.softmax(t[pr["x"]])
+        if self.match.kind in ("w4a16", "sigmoid", "softmax"):
+            x = t[pr["x"]]
+            shape = tuple(x.shape[:-1]) + (t[pr["qweight"]].shape[1],) if self.match.kind == "w4a16" else tuple(x.shape)
+            out = torch.empty(shape, dtype=x.dtype, device=x.device)
+            dt = {torch.float16: "float16", torch.float32: "float32"}[x.dtype]
+            return self.native.forward([t[s.name] for s in self.match.inputs], out, dt)
         if self.match.kind == "eltwise":
             ins = [t[n] for n in pr["inputs"]]
             dt = torch.float32 if any(a.dtype == torch.float32 for a in ins) else torch.float16

@@ -43,14 +43,15 @@ class LlamaConfig:
 _V, _Q, _K, _O, _GATE, _UP, _DOWN, _NORM = range(8)
 
 
-def synth_layer(cfg, layer, centered=False):
-    """Unsharded synthetic weights of one layer (numpy).  centered: zero-mean nibbles (packing.synth_w4)."""
+def synth_layer(cfg, layer, centered=False, scale_mul=1.0):
+    """Unsharded synthetic weights of one layer (numpy).  centered: zero-mean nibbles and scales times
+    scale_mul (packing.synth_w4)."""
     d, f, g = cfg.dim, cfg.ffn, cfg.group
     s = 1000 * layer
     w = {}
     if centered:
         import functools
-        synth = functools.partial(packing.synth_w4, centered=True)
+        synth = functools.partial(packing.synth_w4, centered=True, scale_mul=scale_mul)
         parts = [synth(d, d, s + i, g) for i in (_V, _Q, _K)]
         w["vqk_q"] = np.ascontiguousarray(np.concatenate([p[0] for p in parts], axis=1))
         w["vqk_s"] = np.ascontiguousarray(np.concatenate([p[1] for p in parts], axis=1))
@@ -123,11 +124,11 @@ class SynthWeights:
     """Weight source for LlamaInt4Decoder(weights=...) / the oracle: the seeded synthetic model, optionally
     with zero-mean nibbles (whose greedy stream does not settle on one token)."""
 
-    def __init__(self, cfg, centered=False):
-        self.cfg, self.centered = cfg, bool(centered)
+    def __init__(self, cfg, centered=False, scale_mul=1.0):
+        self.cfg, self.centered, self.scale_mul = cfg, bool(centered), float(scale_mul)
 
     def layer(self, l):
-        return synth_layer(self.cfg, l, self.centered)
+        return synth_layer(self.cfg, l, self.centered, self.scale_mul)
 
     def globals(self):
         return synth_globals(self.cfg)
@@ -191,6 +192,7 @@ class LlamaInt4Decoder:
         self.fused_allreduce = bool(fused_allreduce)  # tensor parallel: sum over ranks inside the O / down projection kernels
         self.launches_per_step = 0
         self._steps_left = 0   # host count of steps the cache and the token log still have room for
+        self.gemv_impl_by_shape = {}
         self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
         self._plist = []
         for w in self.layers:
@@ -205,6 +207,8 @@ class LlamaInt4Decoder:
         2 SiLU(gate)*up; epilogue 0 fp16 / 1 residual += / 2 fp32 partial)."""
         if self.tiled:  # q: [N/128, K/8, 128]
             K, N = q.shape[1] * 8, q.shape[0] * q.shape[2]
+            if self.gemv_impl_by_shape:  # tuning aid: kernel variant per projection shape, {(K, N): gemv_impl}
+                call("ab200_set_option", b"gemv_impl", int(self.gemv_impl_by_shape.get((K, N), 0)))
             call("ab200_w4a16_gemv_tiled", x.data_ptr(), prologue, 0 if norm_w is None else norm_w.data_ptr(), self.cfg.eps,
                  q.data_ptr(), s.data_ptr(), out.data_ptr(), epilogue, 1, K, N, self.cfg.group, self._st)
         else:

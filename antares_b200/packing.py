@@ -36,10 +36,11 @@ def unpack_w4(qweight):
     return out.reshape(Kp * 8, N)
 
 
-def synth_w4(K, N, seed, group=GROUP, scales_dtype=np.float16, centered=False):
+def synth_w4(K, N, seed, group=GROUP, scales_dtype=np.float16, centered=False, scale_mul=1.0):
     """Seeded stand-in for a GPTQ layer: nibbles uniform in 0..15 (drawn as uniform 32-bit words),
     scales uniform in [0.001, 0.02].  centered=True turns every nibble 0 into an 8, so that q - 8 has
-    zero mean (used by tests that need a model whose layers add no common offset)."""
+    zero mean, and scale_mul shrinks the scales (both used by tests that need a model whose layers add
+    no common offset and do not amplify rounding differences)."""
     rng = np.random.default_rng(seed)
     w = rng.integers(0, 2 ** 32, size=(K // 8, N), dtype=np.uint32)
     if centered:
@@ -47,7 +48,10 @@ def synth_w4(K, N, seed, group=GROUP, scales_dtype=np.float16, centered=False):
             zero = ((w >> np.uint32(4 * j)) & np.uint32(15)) == 0
             w |= zero.astype(np.uint32) << np.uint32(4 * j + 3)
     qweight = w.view(np.int32)
-    scales = (rng.random((K // group, N), dtype=np.float32) * np.float32(0.019) + np.float32(0.001)).astype(scales_dtype)
+    scales = rng.random((K // group, N), dtype=np.float32) * np.float32(0.019) + np.float32(0.001)
+    if scale_mul != 1.0:
+        scales *= np.float32(scale_mul)
+    scales = scales.astype(scales_dtype)
     return qweight, scales
 
 

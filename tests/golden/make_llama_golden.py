@@ -7,10 +7,15 @@ on seeded synthetic weights.
                     steps (the layers add a common offset because mean(q - 8) = -0.5).
   p128_n32          the benchmark workload: 128-token prompt + its first 32 generated tokens, same
                     weights; full 32000-entry logits at positions 7, 127 and 158.
-  p8_n32_centered   8-token prompt + 32 generated tokens on zero-mean nibbles (every 0 replaced by 8, test-only
-                    weights): the stream does not settle (>= 20 distinct ids are required here),
-                    so token equality exercises attention, the cache and position handling on
-                    generated steps; full logits at positions 7, 20 and 38.
+  p8_n32_centered   8-token prompt + 32 generated tokens on test-only weights: zero-mean nibbles (every
+                    0 replaced by 8) and scales times 0.25.  Without the common offset the stream does
+                    not settle (>= 12 distinct ids are required here), so token equality exercises
+                    attention, the cache and position handling on generated steps; full logits at
+                    positions 7, 20 and 38.  The smaller scales keep the 32-layer stack from amplifying
+                    rounding differences: with zero-mean nibbles at full scale, Gaussian noise of
+                    5e-4 * max|y| on every projection output moves the logits by 10 % of their maximum
+                    (0.03 % with the benchmark's weights, 1 % with these), so no two correct
+                    implementations could be compared on that model.
 For every step the smallest gap between the best and second-best logit is recorded: a GPU run
 can only be expected to reproduce an id when that gap is well above the numerical tolerance.
 
@@ -52,11 +57,11 @@ def main():
     cfg = LlamaConfig()
     store = {}
     out = {"config": "32 layers, d=4096, 32 heads, ffn 11008, vocab 32000, g=128, eps 1e-6, seeds per antares_b200.llama"}
-    model = OracleLlama(cfg, SynthWeights(cfg, centered=True))
+    model = OracleLlama(cfg, SynthWeights(cfg, centered=True, scale_mul=0.25))
     out["p8_n32_centered"] = run(model, 8, 32, 0, (7, 20, 38), store, "p8_n32_centered")
     gen = out["p8_n32_centered"]["tokens"][8:]
     print(gen, out["p8_n32_centered"]["min_top2_gap"], flush=True)
-    assert len(set(gen)) >= 20, "the centered stream must not settle: %d distinct ids" % len(set(gen))
+    assert len(set(gen)) >= 12, "the centered stream must not settle: %d distinct ids" % len(set(gen))
     del model
     model = OracleLlama(cfg)
     out["p8_n32"] = run(model, 8, 32, 0, (), store, "p8_n32")

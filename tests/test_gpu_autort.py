@@ -136,3 +136,52 @@ def test_exported_elementwise_statements_run_on_the_interpreter(cuda, dtype, n):
         got = autort.ops.gelu_tanh(xd[1:]).float().cpu().numpy()
         want = 0.5 * xr[1:] * (1 + np.tanh(0.7978845608 * (xr[1:] + 0.044715 * xr[1:] ** 3)))
         assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+def test_native_inject_forward_against_oracle(cuda):
+    """Kernel-source text in the reference's wire format -> ab200_inject -> key -> ab200_forward with raw
+    pointers (inputs sorted by name, then the output): W4A16, sigmoid and row softmax against the oracle."""
+    import ctypes
+    from antares_b200 import ops
+    from antares_b200._lib import call
+    st = torch.cuda.current_stream().cuda_stream
+
+    def inject(globals_line, ir):
+        text = ("// GLOBALS: %s\n// BACKEND: c-b200 (default)\n// CONFIG: \n// COMPUTE_V1: - einstein_v2(input_dict={}, extra_outputs=[], exprss=\"%s\")\n"
+                % (globals_line, ir))
+        key = ctypes.c_int(-1)
+        call("ab200_inject", text.encode(), ctypes.cast(ctypes.pointer(key), ctypes.c_void_p))
+        return key.value
+
+    def forward(key, *tensors):
+        args = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        call("ab200_forward", key, ctypes.cast(args, ctypes.c_void_p), len(tensors), st)
+
+    K, N = 4096, 4096
+    qw, sc = packing.synth_w4(K, N, 0)
+    x = packing.synth_x(1, K, 1)
+    ir = "; ".join(s.strip() for s in W4A16_IR.strip().split("\n"))
+    key = inject("input0:float16[%d], qweight:int32[%d, %d], scales:float16[%d, %d] -> my_result:float16[%d]" % (K, K // 8, N, K // 128, N, N), ir)
+    y = torch.empty(N, dtype=torch.float16, device=cuda)
+    forward(key, torch.from_numpy(x[0]).to(cuda), torch.from_numpy(qw).to(cuda), torch.from_numpy(sc).to(cuda), y)
+    assert _err(y.cpu().numpy(), cport.w4a16_gemm(x, qw, sc)[0]) <= 1e-2
+    # 32 rows: the same text family is served by the tensor-core kernel
+    x32 = packing.synth_x(128, K, 2)
+    key = inject("input0:float16[128, %d], qweight:int32[%d, %d], scales:float16[%d, %d] -> my_result:float16[128, %d]" % (K, K // 8, N, K // 128, N, N), ir)
+    y2 = torch.empty((128, N), dtype=torch.float16, device=cuda)
+    forward(key, torch.from_numpy(x32).to(cuda), torch.from_numpy(qw).to(cuda), torch.from_numpy(sc).to(cuda), y2)
+    assert _err(y2.cpu().numpy(), cport.w4a16_gemm(x32, qw, sc)) <= 1e-2
+    rng = np.random.default_rng(3)
+    d = rng.standard_normal(5000).astype(np.float32)
+    key = inject("data:float32[5000] -> sigmoid_f32:float32[5000]", "sigmoid_f32[N] = 1 - 1 / (1 + data[N].call(strs.exp))")
+    o = torch.empty(5000, dtype=torch.float32, device=cuda)
+    forward(key, torch.from_numpy(d).to(cuda), o)
+    assert np.abs(o.cpu().numpy() - cport.sigmoid(d)).max() <= 1e-6
+    s_in = (3 * rng.standard_normal((32, 4096))).astype(np.float16)
+    key = inject("input0:float16[32, 4096] -> output0:float16[32, 4096]",
+                 "temp0[N] >=! input0[N, C]; temp1[N] +=! (input0[N, C] - temp0[N]).call(`exp`); output0[N, C] = (input0[N, C] - temp0[N]).call(`exp`) / temp1[N]")
+    so = torch.empty((32, 4096), dtype=torch.float16, device=cuda)
+    forward(key, torch.from_numpy(s_in).to(cuda), so)
+    assert _err(so.cpu().numpy(), cport.softmax(s_in)) <= 1e-2
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0

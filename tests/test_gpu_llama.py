@@ -130,26 +130,33 @@ def test_benchmark_workload_tokens_and_full_logits(cuda, golden_dir):
 
 
 def test_non_degenerate_stream_matches_the_oracle(cuda, golden_dir):
-    """Zero-mean nibbles (test-only weights): the oracle's greedy stream visits >= 20 distinct ids, so
-    equal ids here say something about attention, the cache and position handling on generated steps.
-    Ids must agree up to the first step whose top-2 logit gap in the oracle is inside the tolerance
-    (after a legitimate near-tie the streams may part); under teacher forcing every step with a clear
-    gap must pick the oracle's id, and the full logits at three positions must be within tolerance."""
+    """Test-only weights (zero-mean nibbles, scales times 0.25): the oracle's greedy stream keeps moving
+    (16 distinct ids among the 32), so equal ids here say something about attention, the cache and
+    position handling on generated steps.  The free-running ids must agree up to the first step whose
+    top-2 logit gap in the oracle is inside the tolerance (after a legitimate near-tie the streams may
+    part); under teacher forcing every step with a clear gap must pick the oracle's id, and the full
+    logits at three positions must be within tolerance.  Tolerance: 2e-2 * max|ref| on this model - a
+    deep stack without the benchmark weights' common offset amplifies rounding differences between any
+    two implementations (measured with the oracle alone: noise of 5e-4 * max|y| on every projection
+    output moves these logits by 1 %, the benchmark model's by 0.03 %)."""
     from antares_b200.llama import SynthWeights
+    tol = 2e-2
     g = json.load(open(os.path.join(golden_dir, "llama_tokens.json")))["p8_n32_centered"]
     lg = np.load(os.path.join(golden_dir, "llama_logits.npz"))
     n_prompt, n_new = g["n_prompt"], g["n_new"]
-    assert len(set(g["tokens"][n_prompt:])) >= 20
+    assert len(set(g["tokens"][n_prompt:])) >= 12
     cfg = LlamaConfig(max_seq=64)
-    dec = LlamaInt4Decoder(cfg, cuda, weights=SynthWeights(cfg, centered=True))
+    dec = LlamaInt4Decoder(cfg, cuda, weights=SynthWeights(cfg, centered=True, scale_mul=0.25))
     prompt = np.array(g["tokens"][:n_prompt], np.int32)
     tokens = list(dec.generate(prompt, n_new))
-    # gaps[i] belongs to the step that chose token n_prompt + i
-    margin = [4 * TOL * m for m in g["logit_abs_max"]]
+    # gaps[i] belongs to the step that chose token n_prompt + i; a choice is "clear" when the oracle's
+    # top-2 gap exceeds twice the logit tolerance (both candidates may move by tol * max|ref|)
+    margin = [2 * tol * m for m in g["logit_abs_max"]]
     clear = [gap > mg for gap, mg in zip(g["top2_gaps"], margin)]
+    assert sum(clear) >= 12, "the golden stream needs enough clear choices to be a check"
     first_unclear = clear.index(False) if False in clear else n_new
-    assert first_unclear >= 8, "the golden stream must start with clear choices"
     assert tokens[:n_prompt + first_unclear] == g["tokens"][:n_prompt + first_unclear]
+    assert len(set(tokens[n_prompt:])) >= 8, "the GPU's own greedy stream must not settle on one id either"
     # teacher forcing over the whole golden stream
     dec.reset(torch.from_numpy(prompt).to(cuda))
     keep = set(g["logits_at"])
@@ -160,7 +167,7 @@ def test_non_degenerate_stream_matches_the_oracle(cuda, golden_dir):
         if pos in keep:
             ref = lg["p8_n32_centered_pos%d" % pos]
             err = np.abs(dec.logits.cpu().numpy() - ref).max() / np.abs(ref).max()
-            assert err <= TOL, "position %d: max|err| = %.3g of max|ref|" % (pos, err)
+            assert err <= tol, "position %d: max|err| = %.3g of max|ref|" % (pos, err)
     assert ops.kernel_status() == 0
 
 

@@ -359,7 +359,7 @@ def test_bulk_ring_gemv_both_layouts(cuda, K, N):
     assert ops.kernel_status() == 0
 
 
-@pytest.mark.parametrize("depth", [2, 4, 16])
+@pytest.mark.parametrize("depth", [4, 8, 16])
 @pytest.mark.parametrize("cluster", [1, 2, 8])
 def test_bulk_ring_gemv_depths_and_clusters(cuda, depth, cluster):
     """Ring depth and K split change only the schedule: wrap-around of the ring (depth below the
@@ -370,6 +370,7 @@ def test_bulk_ring_gemv_depths_and_clusters(cuda, depth, cluster):
     x = packing.synth_x(1, K, 711)
     ref = cport.w4a16_gemm(x, qw, sc)
     y = torch.empty((1, N), dtype=torch.float16, device=cuda)
+    ops.set_option("gemv_impl", 5)
     ops.set_option("ring_depth", depth)
     ops.set_option("gemv_cluster", cluster)
     try:
@@ -377,6 +378,7 @@ def test_bulk_ring_gemv_depths_and_clusters(cuda, depth, cluster):
     finally:
         ops.set_option("ring_depth", 0)
         ops.set_option("gemv_cluster", 0)
+        ops.set_option("gemv_impl", 0)
     assert _err(y.cpu().numpy(), ref) <= TOL
     assert ops.kernel_status() == 0
 
@@ -387,6 +389,7 @@ def test_bulk_ring_gemv_accuracy_on_awkward_activations(cuda):
     qt, st = packing.tile_weights(qw, sc)
     dqt, dst = _dev(qt, cuda), _dev(st, cuda)
     rng = np.random.default_rng(62)
+    ops.set_option("gemv_impl", 5)
     for kind in ("offset", "outlier", "tiny", "huge", "zero"):
         x = rng.standard_normal((1, K))
         x = {"offset": 10 + x, "outlier": np.where(np.arange(K) == 7, 300.0, x), "tiny": x * 1e-4, "huge": x * 2e3, "zero": x * 0}[kind]
@@ -397,3 +400,4 @@ def test_bulk_ring_gemv_accuracy_on_awkward_activations(cuda):
         y = y.cpu().numpy()
         assert np.isfinite(y.astype(np.float32)).all(), kind
         assert np.abs(y.astype(np.float32) - ref.astype(np.float32)).max() <= TOL * max(np.abs(ref.astype(np.float32)).max(), 1e-30), kind
+    ops.set_option("gemv_impl", 0)
