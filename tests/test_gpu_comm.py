@@ -140,6 +140,7 @@ def test_emulated_fused_gemv_allreduce(cuda, world, prologue):
     assert len(set(Ks)) > 1 or world == 2
     bufs = [_alloc(world, n_max) for _ in range(world)]
     ops.set_option("gemv_cluster", 2)  # same K split in the fused and the stand-alone launches: identical partial sums
+    ops.set_option("gemv_impl", 5)     # and the same kernel (the bulk-copy ring GEMV carries the fused exchange)
     try:
         L = _lib.load()
         scratch = torch.zeros(int(L.ab200_w4a16_gemv_emulation_scratch_bytes()), dtype=torch.uint8, device=cuda)
@@ -171,6 +172,7 @@ def test_emulated_fused_gemv_allreduce(cuda, world, prologue):
         assert ops.kernel_status() == 0
     finally:
         ops.set_option("gemv_cluster", 0)
+        ops.set_option("gemv_impl", 0)
         for b in bufs:
             call("ab200_comm_free", b)
 
