@@ -64,6 +64,13 @@ SIGNATURES = {
     "ab200_attention_fused": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp],
     "ab200_silu_mul": [_vp, _vp, _i, _vp],
     "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
+    "ab200_hal_set_device": [_i],
+    "ab200_hal_malloc": [_vp, _sz],
+    "ab200_hal_free": [_vp],
+    "ab200_hal_memcpy": [_vp, _vp, _sz, _i, _vp],
+    "ab200_hal_synchronize": [_vp],
+    "ab200_hal_event_record": [_vp, _vp],
+    "ab200_hal_event_elapsed": [_vp, _vp, _vp],
     "ab200_inject": [ctypes.c_char_p, _vp],
     "ab200_forward": [_i, _vp, _i, _vp],
     "ab200_module_info": [_i, _vp, _vp, _vp, _i],

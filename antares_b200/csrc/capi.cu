@@ -82,3 +82,61 @@ extern "C" int ab200_kernel_status(int *status_host) {
   }
   return AB200_OK;
 }
+
+// ---- device memory, copies and timing for hosts that do not link the CUDA runtime themselves ----------
+// (the `c-b200` HAL header include/c-b200/backend.hpp maps the reference's `namespace ab` onto these)
+
+extern "C" int ab200_hal_set_device(int device) {
+  clear_error();
+  AB200_CUDA(cudaSetDevice(device));
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_malloc(void **ptr_out_host, size_t bytes) {
+  clear_error();
+  AB200_REQUIRE(ptr_out_host != nullptr, "hal_malloc: null output");
+  AB200_CUDA(cudaMalloc(ptr_out_host, bytes));
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_free(void *ptr) {
+  clear_error();
+  AB200_CUDA(cudaFree(ptr));
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_memcpy(void *dst, const void *src, size_t bytes, int kind, void *stream) {
+  clear_error();
+  AB200_REQUIRE(kind >= 0 && kind <= 2, "hal_memcpy: kind %d (0 host->device, 1 device->host, 2 device->device)", kind);
+  const cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+  AB200_CUDA(cudaMemcpyAsync(dst, src, bytes, k, (cudaStream_t)stream));
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_synchronize(void *stream) {
+  clear_error();
+  AB200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_event_record(void **event_out_host, void *stream) {
+  clear_error();
+  AB200_REQUIRE(event_out_host != nullptr, "hal_event_record: null output");
+  cudaEvent_t ev;
+  AB200_CUDA(cudaEventCreate(&ev));
+  AB200_CUDA(cudaEventRecord(ev, (cudaStream_t)stream));
+  *event_out_host = ev;
+  return AB200_OK;
+}
+
+extern "C" int ab200_hal_event_elapsed(void *start_event, void *stop_event, double *seconds_host) {
+  clear_error();
+  AB200_REQUIRE(start_event && stop_event && seconds_host, "hal_event_elapsed: null argument");
+  AB200_CUDA(cudaEventSynchronize((cudaEvent_t)stop_event));
+  float ms = 0.f;
+  AB200_CUDA(cudaEventElapsedTime(&ms, (cudaEvent_t)start_event, (cudaEvent_t)stop_event));
+  AB200_CUDA(cudaEventDestroy((cudaEvent_t)start_event));
+  AB200_CUDA(cudaEventDestroy((cudaEvent_t)stop_event));
+  *seconds_host = ms * 1e-3;
+  return AB200_OK;
+}

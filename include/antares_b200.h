@@ -395,6 +395,24 @@ int ab200_module_tensor(int key, int slot, char *name_host, int name_cap, char *
 int ab200_forward_host_ns(int key, void *const *args_host, int n_args, void *stream, int iters,
                           double *ns_per_call_host);
 
+/* ---- device memory, copies and timing for hosts that do not link the CUDA runtime -------------------
+ * What the reference's HAL offers its runtime next to module loading and launching:
+ * ab::alloc / memcpyHtoD / memcpyDtoH / memcpyDtoD / synchronize / recordTime / convertToElapsedTime
+ * (backends/c-rocm/include/backend.hpp:92-114,221-252).  include/c-b200/backend.hpp maps `namespace ab`
+ * onto these and onto ab200_inject / ab200_forward, so that the reference's evaluator
+ * (graph_evaluator/run_graph.cpp) can drive this library.  All are host calls; the allocating ones
+ * say so in their names. */
+int ab200_hal_set_device(int device);
+int ab200_hal_malloc(void **ptr_out_host, size_t bytes);             /* cudaMalloc */
+int ab200_hal_free(void *ptr);
+/* kind: 0 host->device, 1 device->host, 2 device->device; asynchronous on `stream`. */
+int ab200_hal_memcpy(void *dst, const void *src, size_t bytes, int kind, void *stream);
+int ab200_hal_synchronize(void *stream);
+/* Creates an event and records it on `stream`; ab200_hal_event_elapsed waits for the stop event,
+ * returns the seconds between the two and destroys both. */
+int ab200_hal_event_record(void **event_out_host, void *stream);
+int ab200_hal_event_elapsed(void *start_event, void *stop_event, double *seconds_host);
+
 #ifdef __cplusplus
 }
 #endif

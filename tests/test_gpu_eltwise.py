@@ -123,3 +123,27 @@ def test_attention_fused_matches_unfused_chain(cuda, pos, H):
     assert _err(out.cpu().numpy(), ref) <= TOL
     assert _err(kc_d[pos].cpu().numpy(), kc_ref[pos]) <= TOL and torch.equal(vc_d[pos].cpu(), torch.from_numpy(vc_ref[pos]))
     assert torch.equal(kc_d[pos + 1:].cpu(), torch.from_numpy(kc[pos + 1:])), "rows beyond pos must be untouched"
+
+
+@pytest.mark.parametrize("S", [1, 37, 384])
+def test_attention_against_the_reference_samples_open_statement(cuda, S):
+    """The attention op itself ships closed in the reference, but its tiny-Llama sample states the same
+    math in three open torch lines (samples/03_llama_tiny.py:93-98): scores = einsum('hm,shm->hs', q, K) *
+    att_f; softmax over s; out = einsum('hs,shm->hm', att, V).  Expected values here are exactly those
+    lines in fp32 on the CPU, for 32 heads of 128 and cache lengths 1, 37 and 384 (fp32 and fp16 operands)."""
+    H, D = 32, 128
+    rng = np.random.default_rng(500 + S)
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    k = rng.standard_normal((S, H, D)).astype(np.float32)
+    v = rng.standard_normal((S, H, D)).astype(np.float32)
+    att_f = 1.0 / np.sqrt(D)
+    for dt, tol in ((np.float32, 1e-4), (np.float16, 1e-2)):
+        qd, kd, vd = q.astype(dt), k.astype(dt), v.astype(dt)
+        tq, tk, tv = torch.from_numpy(qd).float(), torch.from_numpy(kd).float(), torch.from_numpy(vd).float()
+        att = torch.einsum('hm,shm->hs', tq, tk) * att_f
+        att = torch.nn.functional.softmax(att, dim=-1)
+        ref = torch.einsum('hs,shm->hm', att, tv).numpy()
+        y = ops.attention_decode(_dev(qd, cuda), _dev(kd.reshape(S, H * D), cuda), _dev(vd.reshape(S, H * D), cuda),
+                                 torch.tensor([S], dtype=torch.int32, device=cuda), att_f)
+        err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
+        assert err <= tol, (dt, err)
