@@ -43,6 +43,7 @@ SIGNATURES = {
     "ab200_w4a16_gemv_prefetch_hint": [_vp, _sz, _vp, _sz],
     "ab200_w4a16_gemv_tiled": [_vp, _i, _vp, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ab200_eltwise_vm": [_vp, _vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _sz, _vp],
+    "ab200_rowreduce_vm": [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "ab200_embed_rows": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ab200_rope_kv_store_rows": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _i, _vp],
     "ab200_attention_prefill": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp],

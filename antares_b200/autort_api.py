@@ -13,9 +13,10 @@ Calling convention kept: tensors positionally in declared order; the result is r
 written into a trailing positional tensor / `out=`; scalars come through `extra=[...]`; dimensions
 declared `Name:val` are upper bounds, the call may pass fewer elements (README.md:64-67).
 `config=` carries tuner hints in the reference ("tune:5", "~N~:[256,8,32],..."): the kernels here
-are hand-scheduled, so it is accepted and ignored.  Single element-wise statements outside the named
-family run on a generic interpreter kernel (ir.compile_elementwise); other IR raises
-NotImplementedError; nothing runs on the CPU.
+are hand-scheduled, so it is accepted and ignored.  Outside the named family, single element-wise
+statements run on a generic interpreter kernel (ir.compile_elementwise) and chains of row reductions
+closed by one map statement (layernorm and the like) on the row-reduction template
+(ir.compile_row_program); other IR raises NotImplementedError; nothing runs on the CPU.
 """
 import torch
 
@@ -153,6 +154,12 @@ def export(ir, inputs, config=None, name=None):
                 dt = torch.float32 if any(a.dtype == torch.float32 for a in ins) else torch.float16
                 out = torch.empty(shape, dtype=dt, device=ins[0].device)
             return _ops.eltwise_program(pr["program"], pr["consts"], ins, out=out)
+    elif match.kind == "rowprog":
+        rp = match.params
+
+        def fn(*tensors, out=None, extra=None):
+            t, out = _split_call(match, tensors, out)
+            return _ops.row_program(rp, [t[n] for n in rp["mats"]], [t[n] for n in rp["cols"]], out=out)
     else:  # pragma: no cover - recognise() raises first
         raise NotImplementedError(match.kind)
     fn.__name__ = match.name

@@ -65,4 +65,6 @@ class CustomOp(torch.nn.Module):
             ins = [t[n] for n in pr["inputs"]]
             dt = torch.float32 if any(a.dtype == torch.float32 for a in ins) else torch.float16
             return _ops.eltwise_program(pr["program"], pr["consts"], ins, out=torch.empty(ins[0].shape, dtype=dt, device=ins[0].device))
+        if self.match.kind == "rowprog":
+            return _ops.row_program(pr, [t[n] for n in pr["mats"]], [t[n] for n in pr["cols"]])
         raise NotImplementedError(self.match.kind)

@@ -79,9 +79,6 @@ _W4_S2 = re.compile(r"^(\w+)\[(\w+),(\w+)\]=(\w+)\[\2/(\d+),\3\]\*\((\w+)\[\2,\3
 _W4_S3 = re.compile(r"^(\w+)\[(\w+)\]\+=(\w+)\[(\w+)\]\*(\w+)\[\4,\2\]\.to\(\3\.dtype\(\)\)$")
 _SIG_README = re.compile(r"^(\w+)\[(\w+)\]=1-1/\(1\+(\w+)\[\2\]\.call\(strs\.exp\)\)$")
 _SIG_CANON = re.compile(r"^(\w+)\[([\w,]+)\]=1\.0/\(1\.0\+\(-(\w+)\[\2\]\)\.call\(`exp`\)\)$")
-_SM_1 = re.compile(r"^(\w+)\[(\w+)\]>=(\w+)\[\2,(\w+)\]$")
-_SM_2 = re.compile(r"^(\w+)\[(\w+)\]\+=\((\w+)\[\2,(\w+)\]-(\w+)\[\2\]\)\.call\(`exp`\)$")
-_SM_3 = re.compile(r"^(\w+)\[(\w+),(\w+)\]=\((\w+)\[\2,\3\]-(\w+)\[\2\]\)\.call\(`exp`\)/(\w+)\[\2\]$")
 
 
 def recognise(ir, inputs, name=None):
@@ -108,10 +105,24 @@ def recognise(ir, inputs, name=None):
                     raise NotImplementedError("W4A16: activations and scales must both be float16 or both float32")
                 return OpMatch("w4a16", op_name, specs, res,
                                dict(x=x1, qweight=qweight, scales=scales, group=int(group), dtype=by_name[x1].dtype))
-        m1, m2, m3 = _SM_1.match(sq[0]), _SM_2.match(sq[1]), _SM_3.match(sq[2])
-        if m1 and m2 and m3 and m1.group(3) == m2.group(3) == m3.group(4) and m2.group(5) == m1.group(1) == m3.group(5) \
-                and m3.group(6) == m2.group(1) and m1.group(3) in by_name:
-            return OpMatch("softmax", op_name, specs, m3.group(1), dict(x=m1.group(3), dtype=by_name[m1.group(3)].dtype))
+    if len(stmts) >= 2:
+        # reduce + map chains: compiled, then either recognised as row softmax by structure (hand-written
+        # kernel) or run on the row-reduction template
+        try:
+            rp = compile_row_program(stmts, [s.name for s in specs])
+        except NotImplementedError as e:
+            row_reason = str(e)
+        else:
+            bad = [n for n in rp["mats"] + rp["cols"] if by_name[n].dtype not in ("float16", "float32")]
+            if bad:
+                row_reason = "row program: %s must be float16 or float32" % ", ".join(bad)
+            elif any(len(by_name[n].dims) != len(rp["axes"]) for n in rp["mats"]) or any(len(by_name[n].dims) != 1 for n in rp["cols"]):
+                row_reason = "row program: operand ranks do not match their indices"
+            elif is_softmax_program(rp) and len(rp["axes"]) == 2:
+                x = rp["mats"][0]
+                return OpMatch("softmax", name or rp["out"], specs, rp["out"], dict(x=x, dtype=by_name[x].dtype))
+            else:
+                return OpMatch("rowprog", name or rp["out"], specs, rp["out"], rp)
     if len(sq) == 1:
         m = _SIG_README.match(sq[0]) or _SIG_CANON.match(sq[0])
         if m and m.group(3) in by_name:
@@ -130,9 +141,10 @@ def recognise(ir, inputs, name=None):
                 return OpMatch("eltwise", name or out_name, specs, out_name, dict(inputs=used, program=prog, consts=consts, axes=axes))
             reason = "element-wise IR: inputs must be float16/float32 tensors of the output's rank"
     else:
-        reason = "multi-statement programs other than the W4A16 and softmax forms are not supported"
+        reason = row_reason if len(stmts) >= 2 else "empty program"
     raise NotImplementedError(
-        "this IR is outside the operator family (W4A16 dequant-matmul, sigmoid, row softmax, single element-wise statements); "
+        "this IR is outside the operator family (W4A16 dequant-matmul, sigmoid, row softmax, single element-wise statements, "
+        "row-reduction chains closed by one map statement); "
         "antares_b200 has no general code generator and no fallback (%s):\n  " % reason + "\n  ".join(stmts))
 
 
@@ -146,7 +158,7 @@ def recognise(ir, inputs, name=None):
 
 VM_OPS = {"in": 0, "const": 1, "add": 2, "sub": 3, "mul": 4, "div": 5, "neg": 6, "exp": 7, "log": 8, "sqrt": 9, "rsqrt": 10,
           "tanh": 11, "erf": 12, "sin": 13, "cos": 14, "abs": 15, "floor": 16, "ceil": 17, "max": 18, "min": 19, "pow": 20,
-          "sigmoid": 21}
+          "sigmoid": 21, "row": 22, "col": 23, "collen": 24}
 _VM_UNARY = ("exp", "log", "sqrt", "rsqrt", "tanh", "erf", "sin", "cos", "abs", "floor", "ceil", "sigmoid")
 _VM_BINARY_CALL = ("max", "min", "pow")
 VM_MAX_OPS, VM_MAX_CONSTS, VM_MAX_INPUTS, VM_MAX_STACK = 48, 16, 8, 8
@@ -174,10 +186,12 @@ def _tokenise(text):
 
 
 class _EltParser:
-    def __init__(self, tokens, axes, input_names):
+    def __init__(self, tokens, axes, input_names, temps=None, cols=None):
         self.t, self.i, self.axes, self.names = tokens, 0, axes, input_names
         self.prog, self.consts, self.used = [], [], []
         self.depth = self.max_depth = 0
+        # row programs only: results of earlier reduction statements (name -> stage), [cols] vectors seen so far
+        self.temps, self.cols = temps, cols
 
     def peek(self):
         return self.t[self.i] if self.i < len(self.t) else ("end", "")
@@ -276,9 +290,12 @@ class _EltParser:
                 self.take()
             self.const((-1 if neg else 1) * float(self.take("num")))
             self.take("sym", ")")
+        elif k == "id" and self.temps is not None and v == self.axes[-1] and self.t[self.i + 1:self.i + 5] == [("sym", "."), ("id", "val"), ("sym", "("), ("sym", ")")]:
+            self.i += 5                      # C.val(): the extent of the reduced axis
+            self.emit("collen", 0, delta=1)
         elif k == "id":
             self.take()
-            if v not in self.names:
+            if v not in self.names and not (self.temps is not None and v in self.temps):
                 raise NotImplementedError("element-wise IR: %r is not a declared input" % v)
             self.take("sym", "[")
             idx = []
@@ -290,11 +307,20 @@ class _EltParser:
                 elif not (kk == "sym" and vv == ","):
                     raise NotImplementedError("element-wise IR: only plain axis indices are supported")
             self.take("sym", "]")
-            if idx != self.axes:
-                raise NotImplementedError("element-wise IR: %s is indexed by %s, the output by %s" % (v, idx, self.axes))
-            if v not in self.used:
-                self.used.append(v)
-            self.emit("in", self.used.index(v), delta=1)
+            if self.temps is not None and v in self.temps:
+                if idx != self.axes[:-1]:
+                    raise NotImplementedError("row program: %s is a row result and must be indexed by %s" % (v, self.axes[:-1]))
+                self.emit("row", self.temps[v], delta=1)
+            elif self.temps is not None and idx == self.axes[-1:] and len(self.axes) > 1:
+                if v not in self.cols:
+                    self.cols.append(v)
+                self.emit("col", self.cols.index(v), delta=1)
+            else:
+                if idx != self.axes:
+                    raise NotImplementedError("element-wise IR: %s is indexed by %s, the output by %s" % (v, idx, self.axes))
+                if v not in self.used:
+                    self.used.append(v)
+                self.emit("in", self.used.index(v), delta=1)
         else:
             raise NotImplementedError("element-wise IR: unexpected %r" % v)
 
@@ -326,28 +352,65 @@ def compile_elementwise(stmt, input_names):
     return out_name, axes, p.used, p.prog, p.consts
 
 
-def eval_program_numpy(prog, consts, arrays):
-    """Reference evaluation of a stack program (numpy, fp32), for the host-side tests."""
-    import numpy as np
-    from math import erf as _erf
-    inv = {v: k for k, v in VM_OPS.items()}
-    st = []
-    f32 = np.float32
-    for op, arg in prog:
-        name = inv[op]
-        if name == "in":
-            st.append(np.asarray(arrays[arg], dtype=f32))
-        elif name == "const":
-            st.append(f32(consts[arg]))
-        elif name in ("add", "sub", "mul", "div", "max", "min", "pow"):
-            b, a = st.pop(), st.pop()
-            st.append({"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide, "max": np.maximum, "min": np.minimum,
-                       "pow": np.power}[name](a, b).astype(f32))
-        else:
-            a = st.pop()
-            fn = {"neg": np.negative, "exp": np.exp, "log": np.log, "sqrt": np.sqrt, "rsqrt": lambda v: 1 / np.sqrt(v), "tanh": np.tanh,
-                  "erf": np.vectorize(_erf, otypes=[f32]), "sin": np.sin, "cos": np.cos, "abs": np.abs, "floor": np.floor, "ceil": np.ceil,
-                  "sigmoid": lambda v: 1 / (1 + np.exp(-v))}[name]
-            st.append(np.asarray(fn(a), dtype=f32))
-    assert len(st) == 1
-    return st[0]
+# ---- reduce + map statement chains over one [rows..., cols] index space ------------------------------------
+# `t0[N] >=! f0(x[N, C]); t1[N] +=! f1(x[N, C], t0[N]); out[N, C] = g(x[N, C], t0[N], t1[N], w[C], C.val())`:
+# the softmax and layernorm forms of AntaresIR.md:226,232.  Every statement's expression becomes a stack
+# program; one kernel (csrc/rowreduce_vm.cu) runs all stages of a row back to back.
+
+ROW_MAX_STAGES, ROW_MAX_MAT, ROW_MAX_COL = 4, 4, 4
+_REDUCE_KIND = {"+": 1, ">": 2, "<": 3}
+
+
+def compile_row_program(stmts, input_names):
+    """Statements -> dict(out, axes, stages=[(kind, program)], consts, mats, cols) with kind 0 map / 1 sum /
+    2 max / 3 min; `mats` are the [axes] inputs and `cols` the [last axis] inputs in operand order.
+    Raises NotImplementedError when the program is not a chain of row reductions closed by one map."""
+    if not 2 <= len(stmts) <= ROW_MAX_STAGES:
+        raise NotImplementedError("row program: 2..%d statements" % ROW_MAX_STAGES)
+    m = re.match(r"^\s*([a-z_]\w*)\s*\[([^\]]*)\]\s*=(?!=)(.*)$", stmts[-1], re.S)
+    if not m:
+        raise NotImplementedError("row program: the last statement must be a plain assignment")
+    out_name, axes_text, rhs_last = m.groups()
+    axes = [a.strip() for a in axes_text.split(",") if a.strip()]
+    if len(axes) < 2 or not all(re.fullmatch(r"[A-Z]\w*", a) for a in axes):
+        raise NotImplementedError("row program: the output must be indexed by two or more plain axes")
+    temps, mats, cols, consts, stages = {}, [], [], [], []
+    depth = 0
+
+    def run(rhs, what):
+        nonlocal depth
+        p = _EltParser(_tokenise(rhs), axes, list(input_names), temps=dict(temps), cols=cols)
+        p.used, p.consts = mats, consts      # operand tables are shared by all stages
+        p.expr()
+        if p.peek()[0] != "end":
+            raise NotImplementedError("row program: trailing text %r in %s" % (p.peek()[1], what))
+        if len(p.prog) > VM_MAX_OPS:
+            raise NotImplementedError("row program: %s is too long for the interpreter (%d operations)" % (what, len(p.prog)))
+        depth = max(depth, p.max_depth)
+        return p.prog
+
+    for i, stmt in enumerate(stmts[:-1]):
+        r = re.match(r"^\s*([a-z_]\w*)\s*\[([^\]]*)\]\s*([+<>])=!?(.*)$", stmt, re.S)
+        if not r:
+            raise NotImplementedError("row program: statement %d is not a +=, >= or <= reduction" % (i + 1))
+        name, idx_text, op, rhs = r.groups()
+        idx = [a.strip() for a in idx_text.split(",") if a.strip()]
+        if idx != axes[:-1]:
+            raise NotImplementedError("row program: %s must be indexed by %s (the output's axes without the reduced one)" % (name, axes[:-1]))
+        stages.append((_REDUCE_KIND[op], run(rhs, "statement %d" % (i + 1))))
+        temps[name] = i
+    stages.append((0, run(rhs_last, "the last statement")))
+    if not mats:
+        raise NotImplementedError("row program: no [%s] input is read" % ", ".join(axes))
+    if len(mats) > ROW_MAX_MAT or len(cols) > ROW_MAX_COL or len(consts) > VM_MAX_CONSTS or depth > VM_MAX_STACK:
+        raise NotImplementedError("row program: too many operands for the interpreter")
+    return dict(out=out_name, axes=axes, stages=stages, consts=consts, mats=mats, cols=cols)
+
+
+def is_softmax_program(rp):
+    """True when a compiled row program is row softmax whatever its tensors are called and however the text
+    is spaced or parenthesised: max of x; sum of exp(x - max); exp(x - max) / sum."""
+    o = VM_OPS
+    sub_exp = [(o["in"], 0), (o["row"], 0), (o["sub"], 0), (o["exp"], 0)]
+    want = [(2, [(o["in"], 0)]), (1, sub_exp), (0, sub_exp + [(o["row"], 1), (o["div"], 0)])]
+    return len(rp["mats"]) == 1 and not rp["cols"] and [(k, list(pr)) for k, pr in rp["stages"]] == want

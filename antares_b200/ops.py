@@ -255,3 +255,39 @@ def eltwise_program(prog, consts, inputs, out=None, out_dtype=None):
     call("ab200_eltwise_vm", ctypes.cast(ops_b, ctypes.c_void_p), ctypes.cast(args_b, ctypes.c_void_p), len(prog), ctypes.cast(cst, ctypes.c_void_p),
          len(consts), ctypes.cast(ptrs, ctypes.c_void_p), ctypes.cast(dts, ctypes.c_void_p), len(inputs), _chk(out, "out"), _code(out.dtype), n, _stream())
     return out
+
+
+def row_program(rp, mats, cols, out=None, out_dtype=None):
+    """Runs a compiled reduce + map chain (ir.compile_row_program) over [..., cols] tensors: `mats` the
+    full-shape inputs, `cols` the [cols] vectors, in the program's operand order."""
+    import ctypes
+    shape = mats[0].shape
+    ncols = shape[-1]
+    rows = mats[0].numel() // ncols
+    for t in mats:
+        if t.shape != shape:
+            raise ValueError("row program: full-shape inputs must share one shape (%s vs %s)" % (tuple(t.shape), tuple(shape)))
+    for t in cols:
+        if t.numel() != ncols:
+            raise ValueError("row program: a column vector must hold %d elements" % ncols)
+    if out is None:
+        dt = out_dtype or (torch.float32 if any(a.dtype == torch.float32 for a in list(mats) + list(cols)) else torch.float16)
+        out = torch.empty(shape, dtype=dt, device=mats[0].device)
+    elif out.numel() != mats[0].numel():
+        raise ValueError("out must hold %d elements" % mats[0].numel())
+    flat = [oa for _, prog in rp["stages"] for oa in prog]
+    ops_b = (ctypes.c_ubyte * len(flat))(*[int(o) for o, _ in flat])
+    args_b = (ctypes.c_ubyte * len(flat))(*[int(a) for _, a in flat])
+    lens = (ctypes.c_int * len(rp["stages"]))(*[len(prog) for _, prog in rp["stages"]])
+    kinds = (ctypes.c_int * len(rp["stages"]))(*[int(k) for k, _ in rp["stages"]])
+    consts = rp["consts"]
+    cst = (ctypes.c_float * max(1, len(consts)))(*[float(c) for c in consts])
+    mp = (ctypes.c_void_p * len(mats))(*[_chk(t, "input") for t in mats])
+    md = (ctypes.c_int * len(mats))(*[_code(t.dtype) for t in mats])
+    cp = (ctypes.c_void_p * max(1, len(cols)))(*[_chk(t, "column vector") for t in cols])
+    cd = (ctypes.c_int * max(1, len(cols)))(*[_code(t.dtype) for t in cols])
+    P = ctypes.c_void_p
+    call("ab200_rowreduce_vm", ctypes.cast(ops_b, P), ctypes.cast(args_b, P), ctypes.cast(lens, P), ctypes.cast(kinds, P), len(rp["stages"]),
+         ctypes.cast(cst, P), len(consts), ctypes.cast(mp, P), ctypes.cast(md, P), len(mats), ctypes.cast(cp, P), ctypes.cast(cd, P), len(cols),
+         _chk(out, "out"), _code(out.dtype), rows, ncols, _stream())
+    return out

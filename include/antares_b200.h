@@ -250,6 +250,22 @@ int ab200_eltwise_vm(const unsigned char *ops_host, const unsigned char *args_ho
                      const int *in_dtypes_host, int n_inputs, void *out, int out_dtype, size_t n,
                      void *stream);
 
+/* Row-reduction template: a chain of row reductions closed by one map statement over one [rows, cols]
+ * index space, e.g. the softmax and layernorm programs of AntaresIR.md:226,232
+ *   t0[N] >=! f0(x[N, C]);  t1[N] +=! f1(x[N, C], t0[N]);  out[N, C] = g(x[N, C], t0[N], t1[N], w[C], C.val())
+ * (the reference generates one kernel per statement, lang/einstein_v2.py:297-578).  Each of the
+ * n_stages (<= 4) statements is a stack program; ops/args hold them back to back, stage_len their
+ * lengths (<= 48 each), stage_reduce their kind (1 sum, 2 max, 3 min; 0 = the final map, which must be
+ * last).  Operation codes as for ab200_eltwise_vm (0 = a [rows, cols] input), plus 22 = row result of
+ * an earlier stage (operand: its index), 23 = a [cols] vector input, 24 = cols as a number.  Inputs and
+ * output AB200_F16 or AB200_F32, arithmetic in fp32, reductions in a fixed order.  Validated on the host. */
+int ab200_rowreduce_vm(const unsigned char *ops_host, const unsigned char *args_host,
+                       const int *stage_len_host, const int *stage_reduce_host, int n_stages,
+                       const float *consts_host, int n_consts, const void *const *mat_inputs_host,
+                       const int *mat_dtypes_host, int n_mat, const void *const *col_inputs_host,
+                       const int *col_dtypes_host, int n_col, void *out, int out_dtype, int rows,
+                       int cols, void *stream);
+
 /* ---- batched (prefill) forms of the glue above: one row per prompt token.  The reference feeds the
  * prompt token by token through the decode step (samples/05_llama2_7b_int4.py:194-200); these let
  * the whole prompt go through ab200_w4a16_gemm instead. ---- */

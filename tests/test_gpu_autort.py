@@ -185,3 +185,29 @@ def test_native_inject_forward_against_oracle(cuda):
     assert _err(so.cpu().numpy(), cport.softmax(s_in)) <= 1e-2
     torch.cuda.synchronize()
     assert ops.kernel_status() == 0
+
+
+def test_layernorm_ir_runs_on_the_row_reduction_template(cuda):
+    """The layernorm program of AntaresIR.md:232 through autort.export (three statements: two row sums and
+    a map), fp32 and fp16, against numpy; and a variant with per-column weight and bias through CustomOp."""
+    ln = ("temp0[N] +=! input0[N, C]; temp1[N] +=! input0[N, C] * input0[N, C]; "
+          "output0[N, C] = (input0[N, C] * C.val() - temp0[N]) * (temp1[N] * C.val() - temp0[N] * temp0[N] + 1e-5).call(`rsqrt`)")
+    f = autort.export(ir=ln, inputs=["input0=float32[N:32, C:1024]"], name="layernorm_f32")
+    x = np.random.default_rng(0).standard_normal((32, 1024)).astype(np.float32) * 2 + 0.5
+    want = (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5 / 1024 ** 2)
+    y = autort.ops.layernorm_f32(torch.from_numpy(x).to(cuda))
+    assert y.dtype == torch.float32 and np.abs(y.cpu().numpy() - want).max() <= 5e-4
+    y2 = f(torch.from_numpy(x[:7]).to(cuda))        # fewer rows than declared: N is a dynamic axis
+    assert np.abs(y2.cpu().numpy() - want[:7]).max() <= 5e-4
+    ir2 = ("s[N] +=! x[N, C]; q[N] +=! x[N, C] * x[N, C]; "
+           "y[N, C] = (x[N, C] - s[N] / C.val()) * (q[N] / C.val() - s[N] / C.val() * s[N] / C.val() + 1e-5).call(`rsqrt`) * g[C] + b[C]")
+    xh = np.random.default_rng(1).standard_normal((2048, 4096)).astype(np.float16)
+    g = np.linspace(0.5, 1.5, 4096).astype(np.float16)
+    b = np.linspace(-1, 1, 4096).astype(np.float16)
+    op = CustomOp(ir=ir2, input_orders={"x": torch.from_numpy(xh), "g": torch.from_numpy(g), "b": torch.from_numpy(b)}, device=cuda).emit()
+    yh = op(torch.from_numpy(xh), torch.from_numpy(g), torch.from_numpy(b))
+    xf = xh.astype(np.float32)
+    want2 = (xf - xf.mean(-1, keepdims=True)) / np.sqrt(xf.var(-1, keepdims=True) + 1e-5) * g.astype(np.float32) + b.astype(np.float32)
+    assert yh.dtype == torch.float16 and _err(yh.cpu().numpy(), want2) <= 1e-2
+    # bitwise repeatable (fixed reduction order)
+    assert torch.equal(op(torch.from_numpy(xh), torch.from_numpy(g), torch.from_numpy(b)), yh)

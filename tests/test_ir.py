@@ -2,6 +2,7 @@
 import pytest
 
 from antares_b200 import ir
+from vm_ref import eval_program_numpy
 
 W4A16_IR = """
   input1[S, N] = (qweight[S / 8, N] >> (S % 8 * 4)).call(strs.bitwise_and, 15) * input0[S].like(1)
@@ -63,14 +64,14 @@ def test_elementwise_statements_compile_to_stack_programs():
     m = ir.recognise(gelu, ["x=float32[N:4096]"])
     assert m.kind == "eltwise" and m.name == "out" and m.params["inputs"] == ["x"]
     x = np.linspace(-4, 4, 33).astype(np.float32)
-    got = ir.eval_program_numpy(m.params["program"], m.params["consts"], [x])
+    got = eval_program_numpy(m.params["program"], m.params["consts"], [x])
     assert np.allclose(got, 0.5 * x * (1 + np.tanh(0.7978845608 * (x + 0.044715 * x ** 3))), atol=1e-6)
     m = ir.recognise("y[A, B] = (a[A, B] - b[A, B]).call(strs.max, [const(0.0)]) / -c[A, B].cast(`float32`) + a[A, B]",
                      ["a=float16[8, 16]", "b=float16[8, 16]", "c=float32[8, 16]"], name="fused")
     assert m.kind == "eltwise" and m.name == "fused" and m.params["inputs"] == ["a", "b", "c"] and m.params["axes"] == ["A", "B"]
     rng = np.random.default_rng(0)
     a, b, c = (rng.standard_normal((8, 16)).astype(np.float32) for _ in range(3))
-    got = ir.eval_program_numpy(m.params["program"], m.params["consts"], [a, b, c])
+    got = eval_program_numpy(m.params["program"], m.params["consts"], [a, b, c])
     assert np.allclose(got, np.maximum(a - b, 0) / -c + a, rtol=1e-6)
 
 
@@ -82,3 +83,55 @@ def test_non_elementwise_statements_are_refused(bad):
     from antares_b200 import ir
     with pytest.raises(NotImplementedError):
         ir.recognise(bad, ["x=float32[N:64]"])
+
+
+LAYERNORM_IR = ("temp0[N] +=! input0[N, C]; temp1[N] +=! input0[N, C] * input0[N, C]; "
+                "output0[N, C] = (input0[N, C] * C.val() - temp0[N]) * (temp1[N] * C.val() - temp0[N] * temp0[N] + 1e-5).call(`rsqrt`)")
+SOFTMAX_IR = ("temp0[N] >=! input0[N, C]; temp1[N] +=! (input0[N, C] - temp0[N]).call(`exp`); "
+              "output0[N, C] = (input0[N, C] - temp0[N]).call(`exp`) / temp1[N]")
+
+
+def test_reduce_map_chains_compile_to_row_programs():
+    """The layernorm program of AntaresIR.md:232 compiles to three stages (sum, sum, map) and evaluates to
+    numpy's layernorm; a variant with a per-column weight and bias uses [C] operands."""
+    import numpy as np
+    from vm_ref import eval_row_program_numpy
+    m = ir.recognise(LAYERNORM_IR, ["input0=float32[N:32, C:1024]"])
+    assert m.kind == "rowprog" and m.output == "output0"
+    rp = m.params
+    assert [k for k, _ in rp["stages"]] == [1, 1, 0] and rp["mats"] == ["input0"] and rp["cols"] == []
+    x = np.random.default_rng(0).standard_normal((32, 1024)).astype(np.float32) * 3 + 1
+    got = eval_row_program_numpy(rp, [x], [])
+    want = (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5 / 1024 ** 2)
+    # the IR's form is (x C - sum) rsqrt(sumsq C - sum^2 + 1e-5): the same as (x - mean) / sqrt(var + 1e-5 / C^2)
+    assert np.abs(got - want).max() <= 2e-4
+    ir2 = ("s[N] +=! x[N, C]; q[N] +=! x[N, C] * x[N, C]; "
+           "y[N, C] = (x[N, C] - s[N] / C.val()) * (q[N] / C.val() - s[N] / C.val() * s[N] / C.val() + 1e-5).call(`rsqrt`) * g[C] + b[C]")
+    m2 = ir.recognise(ir2, ["x=float16[N:8, C:256]", "g=float16[C:256]", "b=float16[C:256]"], name="ln_affine")
+    assert m2.kind == "rowprog" and m2.name == "ln_affine" and m2.params["cols"] == ["g", "b"]
+    x2 = np.random.default_rng(1).standard_normal((8, 256)).astype(np.float32)
+    g, b = np.linspace(0.5, 1.5, 256, dtype=np.float32), np.linspace(-1, 1, 256, dtype=np.float32)
+    got2 = eval_row_program_numpy(m2.params, [x2], [g, b])
+    want2 = (x2 - x2.mean(-1, keepdims=True)) / np.sqrt(x2.var(-1, keepdims=True) + 1e-5) * g + b
+    assert np.abs(got2 - want2).max() <= 1e-4
+
+
+def test_softmax_is_recognised_by_structure_not_by_text():
+    """Whatever the tensors and axes are called, however the text is spaced, parenthesised or split into
+    lines: a max / sum-of-exp / normalise chain is row softmax and gets the hand-written kernel."""
+    for text, decl in ((SOFTMAX_IR, "input0=float16[N:32, C:4096]"),
+                       ("m[R]>=!scores[R,K]\n z[R] += ((scores[R,K]) - m[R]).call(strs.exp)\n p[R,K] = ((scores[R,K] - m[R])).call(`exp`) / (z[R])", "scores=float32[R:4, K:100]")):
+        m = ir.recognise(text, [decl])
+        assert m.kind == "softmax" and m.params["x"] == decl.split("=")[0]
+    # one change of substance and it is a generic row program again
+    m = ir.recognise(SOFTMAX_IR.replace("/ temp1[N]", "/ (temp1[N] + 1.0)"), ["input0=float16[N:32, C:4096]"])
+    assert m.kind == "rowprog"
+
+
+def test_row_program_rejections():
+    with pytest.raises(NotImplementedError):   # the reduced axis is not the last output axis
+        ir.recognise("t[C] +=! x[N, C]; y[N, C] = x[N, C] - t[C]", ["x=float32[N:4, C:8]"])
+    with pytest.raises(NotImplementedError):   # integer tensors
+        ir.recognise("t[N] +=! x[N, C]; y[N, C] = x[N, C] - t[N]", ["x=int32[N:4, C:8]"])
+    with pytest.raises(NotImplementedError):   # a reduction that is not closed by a map statement
+        ir.recognise("t[N] +=! x[N, C]; u[N] +=! x[N, C] * t[N]", ["x=float32[N:4, C:8]"])
