@@ -87,36 +87,59 @@ __global__ void sigmoid_kernel(const T *__restrict__ x, T *__restrict__ out, siz
 }
 
 // ---- RMSNorm -----------------------------------------------------------------------------------
-// One CTA per row; the row stays in registers between the sum of squares and the scaling.
-template <typename T>
+// Persistent CTAs walk the rows with a stride of the grid; a row stays in registers between the sum
+// of squares and the scaling, and the NEXT row's loads are issued before the current row is reduced,
+// so the global-load latency of one row hides behind the reduction and the stores of the one before.
+// The norm weights of a thread's columns are loaded once.  VEC = 8-element vectors per thread.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_rows_kernel(const T *__restrict__ x, const __half *__restrict__ w,
-                                                                  __half *__restrict__ out, int cols, float eps) {
+                                                                  __half *__restrict__ out, int rows, int cols, float eps) {
   __shared__ float sh[32];
-  const size_t row = blockIdx.x;
   const int nvec = cols / 8;
-  float f[ROW_MAX_VEC][8];
-  float ss = 0.f;
+  float wf[VEC][8];
 #pragma unroll
-  for (int v = 0; v < ROW_MAX_VEC; ++v) {
+  for (int v = 0; v < VEC; ++v) {
     const int i = v * ROW_THREADS + threadIdx.x;
-    if (i < nvec) {
-      load8<T>(x + row * cols + (size_t)i * 8, f[v]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += f[v][j] * f[v][j];
-    }
+    if (i < nvec) load8<__half>(w + (size_t)i * 8, wf[v]);
   }
-  ss = block_sum(ss, sh);
-  const float rs = rsqrtf(ss * (1.0f / (float)cols) + eps);
+  float cur[VEC][8], nxt[VEC][8];
+  auto load_row = [&](int row, float (&f)[VEC][8]) {
 #pragma unroll
-  for (int v = 0; v < ROW_MAX_VEC; ++v) {
-    const int i = v * ROW_THREADS + threadIdx.x;
-    if (i < nvec) {
-      float g[8];
-      load8<__half>(w + (size_t)i * 8, g);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = f[v][j] * rs * g[j];
-      store8<__half>(out + row * cols + (size_t)i * 8, g);
+    for (int v = 0; v < VEC; ++v) {
+      const int i = v * ROW_THREADS + threadIdx.x;
+      if (i < nvec) load8<T>(x + (size_t)row * cols + (size_t)i * 8, f[v]);
     }
+  };
+  int row = blockIdx.x;
+  if (row < rows) load_row(row, cur);
+  for (; row < rows; row += gridDim.x) {
+    const int next = row + gridDim.x;
+    if (next < rows) load_row(next, nxt);
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int i = v * ROW_THREADS + threadIdx.x;
+      if (i < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += cur[v][j] * cur[v][j];
+      }
+    }
+    ss = block_sum(ss, sh);
+    const float rs = rsqrtf(ss * (1.0f / (float)cols) + eps);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int i = v * ROW_THREADS + threadIdx.x;
+      if (i < nvec) {
+        float g[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = cur[v][j] * rs * wf[v][j];
+        store8<__half>(out + (size_t)row * cols + (size_t)i * 8, g);
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cur[v][j] = nxt[v][j];
   }
 }
 
@@ -130,26 +153,46 @@ __global__ void rmsnorm_vsum_kernel(const T *__restrict__ x, const float *__rest
 }
 
 // ---- RoPE (rotate-half) ---------------------------------------------------------------------------
-// One CTA per row (= position).  A thread owns 8 consecutive j of the first half and their
-// partners in the second half; the angle depends on (row, j) only, so sin/cos are computed once
-// and reused over the heads the thread walks.
+// One CTA per row (= position).  The angle depends on (row, j) only: D/2 threads compute one sine and
+// cosine each into shared memory while every thread's first operands are already on their way; then a
+// thread owns 8 consecutive j of the first half of some head and their partners in the second half,
+// and walks the heads with a stride of the CTA.
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) rope_kernel(const T *__restrict__ x, const float *__restrict__ inv_freq,
                                                           const int32_t *__restrict__ pos, T *__restrict__ out,
                                                           int H, int D) {
+  __shared__ float sh_c[ROW_THREADS * 8], sh_s[ROW_THREADS * 8];  // D / 2 <= 8 * ROW_THREADS (the host checks D / 16 <= ROW_THREADS)
   const size_t row = blockIdx.x;
   const int half = D / 2, chunks = half / 8;
   const int jc = threadIdx.x % chunks, hslot = threadIdx.x / chunks, hstep = ROW_THREADS / chunks;
-  if (hslot >= hstep) return;
-  const float p = (float)pos[row];
+  float a[8], b[8];
+  const bool active = hslot < hstep && hslot < H;
+  if (active) {
+    const size_t base0 = (row * H + hslot) * (size_t)D + jc * 8;
+    load8<T>(x + base0, a);
+    load8<T>(x + base0 + half, b);
+  }
+  for (int j = threadIdx.x; j < half; j += ROW_THREADS) {
+    float sv, cv;
+    sincosf((float)pos[row] * inv_freq[j], &sv, &cv);
+    sh_s[j] = sv;
+    sh_c[j] = cv;
+  }
+  __syncthreads();
+  if (!active) return;
   float c[8], s[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sincosf(p * inv_freq[jc * 8 + j], &s[j], &c[j]);
+  for (int j = 0; j < 8; ++j) {
+    c[j] = sh_c[jc * 8 + j];
+    s[j] = sh_s[jc * 8 + j];
+  }
   for (int h = hslot; h < H; h += hstep) {
     const size_t base = (row * H + h) * (size_t)D + jc * 8;
-    float a[8], b[8], oa[8], ob[8];
-    load8<T>(x + base, a);
-    load8<T>(x + base + half, b);
+    float oa[8], ob[8];
+    if (h != hslot) {
+      load8<T>(x + base, a);
+      load8<T>(x + base + half, b);
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       oa[j] = a[j] * c[j] - b[j] * s[j];
@@ -388,11 +431,24 @@ extern "C" int ab200_rmsnorm(const void *x, int x_dtype, const void *weight_f16,
                 "rmsnorm: cols=%d must be a multiple of 8, at most %d", cols, ROW_THREADS * ROW_MAX_VEC * 8);
   AB200_REQUIRE(aligned16(x) && aligned16(weight_f16) && aligned16(out_f16), "rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return AB200_OK;
-  if (x_dtype == AB200_F16)
-    rmsnorm_rows_kernel<__half><<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)x, (const __half *)weight_f16, (__half *)out_f16, cols, eps);
-  else if (x_dtype == AB200_F32)
-    rmsnorm_rows_kernel<float><<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const float *)x, (const __half *)weight_f16, (__half *)out_f16, cols, eps);
-  else return fail(AB200_EINVAL, "rmsnorm: unknown dtype %d", x_dtype);
+  AB200_REQUIRE(x_dtype == AB200_F16 || x_dtype == AB200_F32, "rmsnorm: unknown dtype %d", x_dtype);
+  const int vec = (cols / 8 + ROW_THREADS - 1) / ROW_THREADS;  // 8-element vectors per thread
+  const int cap = sm_count() * (vec <= 2 ? 4 : 2);  // persistent CTAs: about what fits an SM by registers
+  const int grid = rows < cap ? rows : cap;
+  const cudaStream_t st = (cudaStream_t)stream;
+#define AB200_RMS_LAUNCH(T, V) rmsnorm_rows_kernel<T, V><<<grid, ROW_THREADS, 0, st>>>((const T *)x, (const __half *)weight_f16, (__half *)out_f16, rows, cols, eps)
+  if (x_dtype == AB200_F16) {
+    if (vec <= 1) AB200_RMS_LAUNCH(__half, 1);
+    else if (vec <= 2) AB200_RMS_LAUNCH(__half, 2);
+    else if (vec <= 4) AB200_RMS_LAUNCH(__half, 4);
+    else AB200_RMS_LAUNCH(__half, 8);
+  } else {
+    if (vec <= 1) AB200_RMS_LAUNCH(float, 1);
+    else if (vec <= 2) AB200_RMS_LAUNCH(float, 2);
+    else if (vec <= 4) AB200_RMS_LAUNCH(float, 4);
+    else AB200_RMS_LAUNCH(float, 8);
+  }
+#undef AB200_RMS_LAUNCH
   AB200_CHECK_LAUNCH("rmsnorm");
   return AB200_OK;
 }
