@@ -517,7 +517,7 @@ def run_ours(args):
     def timed(run_steps):
         """REPEATS x (re-feed the prompt, W warm-up tokens, then exactly K timed steps)."""
         secs = []
-        for _ in range(REPEATS):
+        for _ in range(args.repeats):
             prefill_and_warm()
             fence()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -593,7 +593,7 @@ def run_ours(args):
     if rank != 0:
         return None
     line = {"metric": METRIC, "value": K / sec, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": 1e3 * sec / K, "ms_per_step_min": 1e3 * min(secs) / K, "ms_per_step_max": 1e3 * max(secs) / K, "repeats": REPEATS,
+            "ms_per_step": 1e3 * sec / K, "ms_per_step_min": 1e3 * min(secs) / K, "ms_per_step_max": 1e3 * max(secs) / K, "repeats": args.repeats,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "llama2-7b-arch int4 g128 greedy decode, batch 1, %d prompt tokens then %d timed tokens" % (N_PROMPT, K),
@@ -650,6 +650,7 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=REPEATS, help="how many times the K-step timed region is repeated (median reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the operator-level figures (prefill GEMM, GEMV set)")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 release dependents at kernel start, 2 after the GEMV streaming loop")
