@@ -176,6 +176,5 @@ bool gemv_ring_eligible(int M, int K, int N, int group, bool tiled);
 int gemv_ring_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int K, int N,
                        int epi, bool tiled, cudaStream_t s, void *const *comm_bufs = nullptr, int rank = 0, int world = 1, int n_max = 0);
 int gemv_ring_set_depth(int d);
-int gemv_ring_set_debug(int d);
 
 }  // namespace ab200

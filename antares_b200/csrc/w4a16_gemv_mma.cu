@@ -465,8 +465,7 @@ int gemv_tuning_set(const char *name, int value) {
     g_tune.impl = value;
   } else if (!strcmp(name, "ring_depth")) {
     return gemv_ring_set_depth(value);
-  } else if (!strcmp(name, "ring_debug")) {
-    return gemv_ring_set_debug(value);
+
   } else {
     return fail(AB200_EINVAL, "unknown option %s", name);
   }

@@ -76,7 +76,6 @@ struct RingParams {
   int depth;    // ring stages (a multiple of 4)
   int tiled;    // 1: tile-major weights, linear bulk copies; 0: reference layout, tensor-map copies
   int pdl_late;
-  int debug;    // investigation only: 1 consumers skip the math, 2 no copies beyond the first ring fill and no waits
   float eps;
   unsigned wait_polls;
   // EPI_ALLREDUCE: every rank's receive buffer as mapped here (layout of comm.cu:
@@ -375,7 +374,6 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
       }
       int slot = 0, round = 0;
       for (int s = 0; s < nst; ++s) {
-        if ((p.debug & 2) && round > 0) break;
         if (round > 0 && !r_mbar_wait(bars + 8 * (D + slot), (round - 1) & 1, p.wait_polls)) {
           atomicExch(p.status, 400 + slot);  // site 400: a ring stage was never released
           break;
@@ -432,7 +430,6 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
     uint32_t c_addr = r_smem_u32(corr) + (uint32_t)((pr * 4 + hf * 2) * 4);
     uint32_t s_addr = r_smem_u32(sc_s) + (uint32_t)(pr * R_SCALE_ROW_BYTES + lane * 8);
     unsigned parity = 0;
-    const bool free_run = (p.debug & 2) != 0;
     constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
     // The barrier of the NEXT visit is probed (test_wait: never blocks) right after this visit's words
     // are in registers, so the probe's latency hides behind the multiply-adds; `ready` carries the
@@ -441,7 +438,7 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
     if (pr < nst) asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                                : "=r"(ready) : "r"(full_addr), "r"(parity) : "memory");
     for (int s = pr; s < nst; s += 4) {
-      if (!ready && !(free_run && s >= D) && !r_mbar_wait_slow(full_addr, parity, p.wait_polls)) {
+      if (!ready && !r_mbar_wait_slow(full_addr, parity, p.wait_polls)) {
         if (lane == 0) atomicExch(p.status, 410 + pr);  // site 410: a ring stage never arrived
         break;                                          // stop waiting; the result is void
       }
@@ -468,9 +465,7 @@ __global__ void __launch_bounds__(R_THREADS) w4a16_gemv_ring_kernel(const __grid
         if (s + 4 < nst) asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                                       : "=r"(ready) : "r"(full_addr), "r"(parity) : "memory");
       }
-      if (p.debug & 1) {
-        facc[0] += __uint_as_float(wv[0].x ^ wv[1].y ^ wv[2].z ^ wv[3].w ^ wv[4].x ^ wv[5].y ^ wv[6].z ^ wv[7].w);
-      } else {
+      {
         const float2 s01 = __half22float2(u2h2(sv.x)), s23 = __half22float2(u2h2(sv.y));
         const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
 #pragma unroll
@@ -588,8 +583,7 @@ typedef CUresult (*RingEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static int g_ring_depth = 0;             // 0 = auto
-static int g_ring_debug = 0;
-int gemv_ring_set_debug(int d) { g_ring_debug = d; return AB200_OK; }
+
 static unsigned g_ring_wait_polls = 1u << 22;
 
 int gemv_ring_set_depth(int d) {
@@ -690,7 +684,6 @@ static int ring_params(RingParams &p, const void *x, const __half *norm_w, float
   p.depth = depth;
   p.tiled = tiled ? 1 : 0;
   p.pdl_late = pdl_mode() == 2;
-  p.debug = g_ring_debug;
   p.eps = eps;
   p.wait_polls = g_ring_wait_polls;
   return AB200_OK;
