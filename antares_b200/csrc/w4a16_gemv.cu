@@ -1,23 +1,28 @@
 // W4A16 decode GEMV for sm_100a: out[M,N] = x[M,K] . dequant(qweight[K/8,N], scales[K/group,N]).
-// Scalar-pipe variant (no tensor cores) for fp16, selectable with option gemv_impl=1, and the
-// fp32 variant; the default fp16 path is the warp-MMA kernel in w4a16_gemv_mma.cu.
+// Register-prefetch scalar-pipe kernel (no tensor cores): the default for one batch row (and for up to
+// four rows on the tile-major layout), plus the fp32 variant and the host-side choice among the GEMV
+// kernels (batch 2-16: TMA ring + warp MMA, w4a16_gemv_tma.cu; bulk-copy ring, w4a16_gemv_ring.cu, on
+// request and for the tensor-parallel fused exchange).
 //
 // Replaces the kernel the reference generates from samples/05_llama2_7b_int4.py:135-139.
 //
-// Data layout in HBM (unchanged from the reference: no repacking is needed to stream it):
-//   qweight int32 [K/8, N], N contiguous: one 16-byte load = 4 columns x 8 k-values; a warp
-//   reads 512 contiguous bytes of one packed row (128 columns).
-//   scales fp16/fp32 [K/group, N]; x [M, K]; out [M, N].
+// Data layout in HBM: the reference's, qweight int32 [K/8, N], N contiguous (one 16-byte load = 4 columns
+// x 8 k-values; a warp reads 512 contiguous bytes of one packed row), scales fp16/fp32 [K/group, N]; or
+// tile-major [N/128][K/8][128] (ab200_w4a16_gemv_tiled), where what one CTA streams is one contiguous range.
 //
-// Decomposition: CTA = 128 columns x a contiguous slice of K; its 8 warps take 32-k "units"
-// (4 packed rows) round-robin, with two units' loads (8 x 16 B per thread) in flight, the first
-// ones issued before x is staged.  The K slices of one column tile are the CTAs of one thread-block cluster; the
-// partial sums meet in distributed shared memory in a fixed order (deterministic, no global
-// scratch, no atomics).  HBM-bound: algorithmic bytes = K*N/2 + (K/group)*N*2 + M*K*2 + M*N*2.
+// Decomposition: CTA = 128 columns x a contiguous slice of K; its 8 warps take 32-k "units" (4 packed
+// rows) round-robin, with two units' loads (8 x 16 B per thread) in flight in registers, the first ones
+// issued before griddepcontrol.wait and before x is staged.  The K slices of one column tile are the CTAs
+// of one thread-block cluster; every CTA pushes its column sums into the owner CTA's inbox through
+// distributed shared memory (split cluster barrier: arrive at kernel start, wait before the first remote
+// store), one cluster barrier, rank-ordered sum (deterministic, no global scratch, no atomics).
+// HBM-bound by design: algorithmic bytes = K*N/2 + (K/group)*N*2 + M*K*2 + M*N*2.
 //
-// fp16 path arithmetic: nibbles become fp16 (q-8) exactly (0x6400 magic + one HSUB2/HFMA2),
-// 16 products per column lane are chained in HFMA2, then widened to fp32 and multiplied by the
-// group scale; everything across units, warps and CTAs is fp32.
+// fp16 arithmetic (raw-nibble multiply): `w & 0x000F000F` is a pair of fp16 subnormals q * 2^-24
+// (`w & 0x00F000F0` = 16 q * 2^-24); they are multiplied on the FP16 pipe by activations pre-scaled by a
+// power of two chosen per batch row (the words that meet high nibbles by another 1/16), 16 products per
+// half2 lane, then widened to fp32; the zero-point leaves the inner loop as 8 * sum(x) per 32-k unit,
+// subtracted in fp32 before the group scale is applied; everything across units, warps and CTAs is fp32.
 #include <cooperative_groups.h>
 
 #include "common.cuh"

@@ -288,7 +288,7 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
     gate_up_alg = cfg.dim * 2 * dec.fl // 2 + (cfg.dim // cfg.group) * 2 * dec.fl * 2 + cfg.dim * 2 + 2 * dec.fl * 2
     if dec.world == 1:
         traffic = NCU_TRAFFIC_GATE_UP
-        note = ("DRAM bytes of ONE unsharded gate|up launch from an ncu capture of that kernel (profiles/), not measured by this run; "
+        note = ("DRAM bytes of ONE unsharded gate|up launch from an ncu capture of that kernel, quoted, not measured by this run; "
                 "algorithmic bytes of that launch: %d" % gate_up_alg)
     else:
         traffic = None
@@ -299,8 +299,8 @@ def gemv_roofline(dec, torch, peak_gbs, peak_kind):
 
 
 def extras_single_ops(torch, dev, peak_gbs, tensor_peak):
-    """Operator-level figures next to the headline (rank 0, N=1): the W4A16 prefill GEMM of BASELINE
-    config 3 on the tensor cores and the four decode GEMV shapes of config 2 at batch 1, 8 and 16, each timed
+    """Operator-level figures next to the headline (rank 0, N=1): the W4A16 prefill GEMM (x fp16
+    [2048, 4096], W 4096 -> 11008) on the tensor cores and the four decode GEMV shapes at batch 1, 8 and 16, each timed
     alone with CUDA events (GEMVs rotate through weight copies larger than L2)."""
     import numpy as np
     from antares_b200 import ops, packing

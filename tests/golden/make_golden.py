@@ -4,7 +4,7 @@ c-mcpu runtime (oracle/refrt.py).  Needs the reference checkout (to build oracle
   python tests/golden/make_golden.py
 
 The fixtures hold inputs AND outputs, so the tests that read them need neither the reference nor
-the same random generator.  `c0_digest.json` pins the full-size BASELINE config 0
+the same random generator.  `c0_digest.json` pins the full-size 4096x4096 fp16 case
 (x fp16 [1,4096], W 4096x4096, g=128, seed 0) by the evaluator's digest formula
 (graph_evaluator/run_graph.cpp:189-209) and a sha256 of the fp16 output bytes.
 """
@@ -81,7 +81,7 @@ def main():
     refrt.RefModule(rk.attention(S, H, D, S))(att_f, kc, qv, vc, y)
     np.savez_compressed(os.path.join(HERE, "attention_f16_s37_h4.npz"), q=qv, k=kc, v=vc, scale=att_f, y=y)
 
-    # BASELINE config 0 at full size
+    # the 4096x4096 fp16 case at full size
     qw, sc = packing.synth_w4(4096, 4096, 0)
     x = packing.synth_x(1, 4096, 1)
     y = np.zeros((1, 4096), np.float16)

@@ -1,4 +1,4 @@
-"""GPU parity tests of the elementwise / reduction operators (BASELINE config 1 shapes and the
+"""GPU parity tests of the elementwise / reduction operators (the benchmark's element-wise / reduction shapes and the
 golden vectors of the reference runtime).  Tolerance: max|err| <= 1e-2 * max|ref|."""
 import os
 

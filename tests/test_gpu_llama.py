@@ -1,5 +1,5 @@
 """GPU parity of the full decode step against the CPU oracle: logits within 1e-2 * max|ref| under
-teacher forcing, and identical greedy token ids (BASELINE config 4 correctness bar)."""
+teacher forcing, and identical greedy token ids (the full-decode workload's correctness bar)."""
 import json
 import os
 

@@ -80,7 +80,7 @@ def test_gemv_fp32_matches_oracle(cuda, M, K, N):
 
 
 def test_c0_full_size_against_reference_digest(cuda, golden_dir):
-    """BASELINE config 0: x fp16 [1,4096], W 4096x4096, g=128."""
+    """The reference's CPU-runnable case: x fp16 [1,4096], W 4096x4096, g=128."""
     info = json.load(open(os.path.join(golden_dir, "c0_digest.json")))
     qw, sc = packing.synth_w4(4096, 4096, 0)
     x = packing.synth_x(1, 4096, 1)
@@ -95,7 +95,7 @@ def test_c0_full_size_against_reference_digest(cuda, golden_dir):
 @pytest.mark.parametrize("K,N", [(4096, 12288), (4096, 4096), (4096, 22016), (11008, 4096)])
 @pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
 def test_llama_gemv_set(cuda, K, N, M):
-    """BASELINE config 2: the four Llama-2-7B projections at batch 1..16."""
+    """The decode GEMV set: the four Llama-2-7B projections at batch 1..16."""
     qw, sc = packing.synth_w4(K, N, K + N)
     x = packing.synth_x(M, K, M)
     ref = cport.w4a16_gemm(x, qw, sc)
@@ -198,7 +198,7 @@ def test_prefill_gemm_tcgen05_matches_oracle(cuda, M, K, N):
 
 
 def test_prefill_gemm_config3_full_size(cuda):
-    """BASELINE config 3: x fp16 [2048, 4096], W 4096 -> 11008, g=128.  All rows computed on the GPU; a
+    """The prefill GEMM workload: x fp16 [2048, 4096], W 4096 -> 11008, g=128.  All rows computed on the GPU; a
     seeded sample of 64 rows is checked against the oracle, the rest through linearity."""
     M, K, N = 2048, 4096, 11008
     qw, sc = packing.synth_w4(K, N, 61)
