@@ -161,6 +161,16 @@ bool gemv_tma_eligible(int dtype, int M, int K, int N, int group);
 int gemv_tma_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
                       int K, int N, int group, int epi, cudaStream_t s, bool *handled);
 
+// TMA ring with the activations streamed through it (w4a16_gemv_slab.cu): batch 5-16
+bool gemv_slab_eligible(int dtype, int M, int K, int N, int group);
+int gemv_slab_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
+                       int K, int N, int group, int epi, cudaStream_t s, bool *handled);
+
+// tcgen05 variant, weights as the A operand in tensor memory (w4a16_gemv_tc.cu): batch 1-16
+bool gemv_tc_eligible(int dtype, int M, int K, int N, int group);
+int gemv_tc_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M, int K,
+                     int N, int group, int epi, cudaStream_t s, bool *handled);
+
 // persistent balanced variant (w4a16_gemv_persist.cu)
 enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_SILU_MUL = 2 };
 constexpr size_t PERSIST_COUNTER_BYTES = 64 * 1024;  // counters live at the start of the scratch: up to 16384 column tiles

@@ -602,8 +602,9 @@ static int gemv_f16_scalar(GemvParams p, int M, int epi, cudaStream_t s) {
 }
 
 // fp16 path.  Auto choice (measured on B200): one row on the scalar-pipe cluster kernel (lowest
-// fixed cost and best streaming rate at that size); 2-16 rows on the TMA-ring warp-MMA kernel
-// (cost nearly constant in the batch size) when the shape fits it (group 128, N % 8 == 0), else
+// fixed cost and best streaming rate at that size); 2-16 rows on the TMA-ring warp-MMA kernels
+// (activations resident in shared memory, or streamed through the ring for wide projections at
+// 5-16 rows) when the shape fits them (group 128, N % 8 == 0), else
 // 3-16 rows on the cluster warp-MMA kernel, else the scalar-pipe kernel.  The persistent warp-MMA kernel (option gemv_impl=3)
 // needs scratch; scratch == nullptr means the library-owned buffer.
 // One-shot prefetch hint of the calling thread (ab200_w4a16_gemv_prefetch_hint): consumed by the
@@ -633,6 +634,18 @@ static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps
   }
   if (impl == 5 && gemv_ring_eligible(M, K, N, group, false))
     return gemv_ring_dispatch(x, pro, norm_w, eps, qw, scales, out, K, N, epi, false, s);
+  if (impl == 7) {
+    bool handled = false;
+    const int rc = gemv_tc_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
+    if (rc || handled) return rc;
+  }
+  // streamed activations: measured faster than the resident-activation TMA kernel for wide projections at 9-16
+  // rows (gate|up at 16 rows: 20 us against 33) and for the widest at 5-8 rows
+  if (impl == 6 || (impl == 0 && ((M >= 9 && N >= 8192) || (M >= 5 && N >= 16384)))) {
+    bool handled = false;
+    const int rc = gemv_slab_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
+    if (rc || handled) return rc;
+  }
   if (impl == 4 || (impl == 0 && M >= 2)) {
     bool handled = false;
     const int rc = gemv_tma_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);

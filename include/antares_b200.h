@@ -49,7 +49,8 @@ int ab200_kernel_status(int *status_host);
 /* Tuning knobs, the counterpart of the `config=` hints of autort.export
  * (samples/05_llama2_7b_int4.py:139).  Names: "gemv_cluster" (0 = auto, 1/2/4/8 K-slices per
  * column tile), "gemv_impl" (0 auto, 1 scalar pipes only, 2 cluster warp-MMA, 3 persistent warp-MMA,
- * 4 TMA ring + warp-MMA, 5 bulk-copy ring for batch 1),
+ * 4 TMA ring + warp-MMA, 5 bulk-copy ring for batch 1, 6 TMA ring with streamed activations for batch 5-16,
+ * 7 tcgen05 MMA with the dequantised weights written to tensor memory),
  * "gemv_depth" (0 auto, 2..6 units of prefetch per warp in the cluster warp-MMA kernel),
  * "ring_depth" (0 auto, even 2..16: 8 KiB stages per CTA in the bulk-copy ring kernel).
  * "comm_wait_polls": polls after which the push all-reduce gives up waiting for a peer.

@@ -184,6 +184,41 @@ def test_fused_rmsnorm_prologue_and_residual_epilogue(cuda, M):
     assert _err(resid.cpu().numpy(), ref2) <= TOL
 
 
+@pytest.mark.parametrize("M,K,N", [(5, 4096, 4096), (8, 4096, 22016), (16, 4096, 22016), (16, 11008, 4096), (13, 4096, 12288),
+                                   (9, 1408, 2752), (16, 128, 136), (7, 384, 4096)])
+@pytest.mark.parametrize("impl", [6, 7])
+def test_streamed_activation_gemv_matches_oracle(cuda, impl, M, K, N):
+    """Batches of 5-16 rows on the two kernels that stream the activations through the TMA ring with the
+    weights (option gemv_impl=6: warp MMA; 7: tcgen05 with the weights in tensor memory): every prologue and
+    epilogue against the oracle, twice back to back (the second call's activation slabs overwrite the
+    first's), bitwise repeatable."""
+    qw, sc = packing.synth_w4(K, N, 131)
+    rng = np.random.default_rng(132)
+    x16 = packing.synth_x(M, K, 133)
+    x32 = (rng.standard_normal((M, K)) * 3).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal(K)).astype(np.float16)
+    gu = rng.standard_normal((M, 2 * K)).astype(np.float16)
+    h = np.stack([cport.silu_mul(gu[m, :K].copy(), gu[m, K:].copy()) for m in range(M)])
+    resid0 = rng.standard_normal((M, N)).astype(np.float32)
+    dq, ds = _dev(qw, cuda), _dev(sc, cuda)
+    ops.set_option("gemv_impl", impl)
+    try:
+        y = ops.w4a16_gemv(_dev(x16, cuda), dq, ds)
+        y2 = ops.w4a16_gemv(_dev(x16, cuda), dq, ds)
+        yn = torch.empty((M, N), dtype=torch.float16, device=cuda)
+        ops.w4a16_gemv_fused(_dev(x32, cuda), dq, ds, yn, prologue=ops.PRO_RMSNORM, norm_weight=_dev(wn, cuda), eps=1e-6)
+        resid = _dev(resid0, cuda)
+        ops.w4a16_gemv_fused(_dev(gu, cuda), dq, ds, resid, prologue=ops.PRO_SILU_MUL, epilogue=ops.EPI_RESIDUAL)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_option("gemv_impl", 0)
+    assert ops.kernel_status() == 0
+    assert _err(y.cpu().numpy(), cport.w4a16_gemm(x16, qw, sc)) <= TOL
+    assert torch.equal(y, y2), "results must be bitwise repeatable"
+    assert _err(yn.cpu().numpy(), cport.w4a16_gemm(cport.rmsnorm(x32, wn, 1e-6), qw, sc)) <= TOL
+    assert _err(resid.cpu().numpy(), resid0 + cport.w4a16_gemm(h, qw, sc).astype(np.float32)) <= TOL
+
+
 @pytest.mark.parametrize("M,K,N", [(128, 128, 256), (256, 512, 512), (130, 256, 264), (17, 4096, 1000), (384, 11008, 512)])
 def test_prefill_gemm_tcgen05_matches_oracle(cuda, M, K, N):
     """W4A16 GEMM on tcgen05/TMEM: same arithmetic as the decode path, M beyond 16, ragged tiles."""
