@@ -463,9 +463,6 @@ int gemv_tuning_set(const char *name, int value) {
     if (value < 0 || value > 7)
       return fail(AB200_EINVAL, "gemv_impl must be 0 (auto), 1 (scalar pipes), 2 (cluster warp MMA), 3 (persistent warp MMA), 4 (TMA ring + warp MMA), 5 (bulk-copy ring, batch 1), 6 (TMA ring with streamed activations, batch 5-16) or 7 (tcgen05 with the weights in tensor memory)");
     g_tune.impl = value;
-  } else if (!strcmp(name, "tc_debug")) {
-    extern int g_tc_debug;
-    g_tc_debug = value;
   } else if (!strcmp(name, "ring_depth")) {
     return gemv_ring_set_depth(value);
 

@@ -1,8 +1,8 @@
-// W4A16 decode GEMV for batches of 5-16 rows on the 5th-generation tensor cores (fp16, group 128):
-// weights^T is the MMA's A operand, written straight into tensor memory; the activations are the B operand.
+// W4A16 decode GEMV on the 5th-generation tensor cores (fp16, group 128, 1-16 batch rows): weights^T is
+// the MMA's A operand, written straight into tensor memory; the activations are the B operand.
+// Opt-in (option gemv_impl=7): measured slower than the warp-MMA kernels at these batch sizes, see below.
 //
-// Replaces the kernel the reference generates from samples/05_llama2_7b_int4.py:135-139 when it is called
-// with 5..16 batch rows.
+// Replaces the kernel the reference generates from samples/05_llama2_7b_int4.py:135-139.
 //
 // y^T[n, m] = sum_k W[k, n] x[m, k]: a 128-column tile of the weight matrix gives the 128 rows of a
 // `tcgen05.mma.cta_group::1.kind::f16` (M128 N16 K16), the (zero-padded) 16 batch rows give its N.  A packed
@@ -14,19 +14,28 @@
 // never passes through shared memory.  The activations come from a small kernel that writes them once in the
 // matching k order, the odd pairs divided by 16, as the K-major core-matrix layout the MMA reads from shared
 // memory, one slab per 256-k stage, followed by the accumulator corrections -8 * 2^-24 * sum_k x per
-// quantisation group; a slab travels through the TMA ring with the stage's weights and scales.
+// quantisation group; slabs and scales travel through one TMA ring, the packed weights through another (a
+// weight stage is free as soon as its words are in registers, an activation stage only when its MMAs are done).
 //
 // The tensor core accumulates one quantisation group (128 k = 8 MMAs) in its own 16 TMEM columns; four
 // warps read a finished group back (`tcgen05.ld`), add the correction, multiply by the column's scale and
 // add into fp32 registers, while the MMAs of the next group run into the other accumulator.
 //
-// Roles in a CTA of 14 warps: 2 x 4 warps dequantise (group 0 / group 1 of every stage), 4 warps drain
-// accumulators, 1 thread runs the TMA ring, 1 thread issues the MMAs.  They meet only through mbarriers.
+// Roles in a CTA of 16 warps: 2 x 4 warps dequantise (group 0 / group 1 of every stage), 4 warps drain
+// accumulators, 1 thread runs the TMA rings, 2 threads issue the MMAs (one per group), 1 warp moves finished
+// sums to global memory.  They meet only through mbarriers.
 //
 // Work split: persistent CTAs, two per SM.  The (tile, stage) units in tile-major order are cut into equal
 // contiguous ranges, one per CTA; a CTA that finishes its part of a tile stores the partial sums, the last CTA
 // to arrive at the tile adds the partials in range order (bitwise repeatable) and writes the output.
-// Every wait is bounded (status sites 600-660).
+// Every wait is bounded (status sites 600-680).
+//
+// Measured on B200 (gate|up projection 4096 x 22016, isolated, cold weights): 24 us at 1 row, 30 us at 16,
+// against 11 us (scalar kernel, 1 row) and 20 us (warp-MMA ring kernel, 16 rows).  Device timestamps show the
+// two MMA-issuing threads as the limit: an M128 N16 K16 instruction costs its issuing thread about 100 cycles
+// and a 256-k stage needs 16 of them (about 1800 cycles per stage and CTA, 9 stages per CTA), and the
+// exchange of partial sums adds 3-5 us at the end.  The instruction count does not depend on N, so the
+// same structure would pay off only at batch sizes well beyond 16.
 #include <cuda.h>  // CUtensorMap (types only)
 
 #include "common.cuh"
@@ -35,14 +44,16 @@
 namespace ab200 {
 
 constexpr int C_DQ_WARPS = 8, C_DRAIN_WARPS = 4;
-constexpr int C_PRODUCER_WARP = 12, C_ISSUER_WARP = 13;
-constexpr int C_THREADS = 14 * 32;
+constexpr int C_PRODUCER_WARP = 12, C_ISSUER_WARP = 13, C_FLUSH_WARP = 15;  // issuers: warps 13 and 14
+constexpr int C_THREADS = 16 * 32;
 constexpr int C_MB = 16;                          // batch rows of the MMA (N)
 constexpr int C_W_BYTES = 32 * TILE_N * 4;        // 32 packed rows x 128 columns
 constexpr int C_SC_BYTES = 2 * TILE_N * 2;        // two scale rows
 constexpr int C_X_BYTES = 32 * 2 * 128;           // 32 chunks of 8 k x 2 row groups x (8 rows x 16 B)
 constexpr int C_SLAB = C_X_BYTES + 2 * C_MB * 4;  // + corrections [2 groups][16]
-constexpr int C_STAGE = C_W_BYTES + C_SC_BYTES + C_SLAB;  // 25216 = 197 * 128
+constexpr int C_XSTAGE = C_SC_BYTES + C_SLAB;     // stage of the activation ring: scales | x | corrections = 8832 = 69 * 128
+constexpr int C_DW = 3, C_DX = 5;                 // ring depths: weights (16 KiB stages, held until read into registers),
+                                                  // activations (held until the stage's MMAs are complete and drained)
 constexpr int C_MAX_DEPTH = 8;
 constexpr int C_NA = 3;                           // A buffers (64 k = 32 TMEM columns each) per dequantising warp group
 constexpr int C_ND = 2;                           // accumulators (16 TMEM columns each) per group of a stage
@@ -136,16 +147,22 @@ struct TcGemvParams {
   int M, N;
   int S;       // stages per tile = ceil(K / 256)
   int U;       // tiles * S
-  int depth;   // ring stages
   int max_cnt; // partial slots per tile
   unsigned wait_polls;
-  int debug;
-  long long *trace;
 };
 
 __device__ __forceinline__ uint32_t c_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ bool c_mbar_wait(uint32_t bar, unsigned parity, unsigned polls) {
+  {  // non-blocking probe first: the common case is a phase that completed long ago
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (unsigned i = 0; i < polls; ++i) {
     uint32_t done;
     asm volatile(
@@ -173,37 +190,62 @@ __device__ __forceinline__ uint64_t c_desc(uint32_t smem_addr, uint32_t lbo_byte
   return d;
 }
 
-#define C_TRACE(role, i, k)                                                                           \
-  do {                                                                                                \
-    if (p.trace && blockIdx.x == 0 && lane == 0 && (i) < 16) p.trace[((role)*16 + (i)) * 8 + (k)] = clock64(); \
-  } while (0)
+// D[tmem_d] (+)= A[tmem_a] . B[desc]: M128 N16 K16, A from tensor memory
+template <bool ACCUMULATE>
+__device__ __forceinline__ void c_mma(uint32_t tmem_d, uint32_t tmem_a, uint64_t db) {
+  if (ACCUMULATE)
+    asm volatile("{\n .reg .pred p;\n setp.eq.u32 p, 0, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n}\n" ::"r"(tmem_d),
+                 "r"(tmem_a), "l"(db), "r"(C_IDESC), "r"(0u)
+                 : "memory");
+  else
+    asm volatile("{\n .reg .pred p;\n setp.ne.u32 p, 0, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n}\n" ::"r"(tmem_d),
+                 "r"(tmem_a), "l"(db), "r"(C_IDESC), "r"(0u)
+                 : "memory");
+}
+
+// The CTAs whose unit ranges meet tile t: first, count
+// (U * G fits 32 bits: the host checks it)
+__device__ __forceinline__ void c_tile_parts(unsigned U, unsigned G, unsigned S, unsigned t, int &first, int &cnt) {
+  const unsigned a = t * S, b = a + S - 1;
+  unsigned bf = a * G / U, bl = b * G / U;
+  while (bf + 1 < G && U * (bf + 1) / G <= a) ++bf;
+  while (bl + 1 < G && U * (bl + 1) / G <= b) ++bl;
+  first = (int)bf;
+  cnt = (int)(bl - bf) + 1;
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_s,
                                                                       TcGemvParams p) {
   extern __shared__ unsigned char c_smem[];
-  // barriers: full[8] empty[8] aready[2][NA] afree[2][NA] dready[2][ND] dfree[2][ND]
-  __shared__ __align__(8) unsigned long long sh_bars[2 * C_MAX_DEPTH + 4 * C_NA + 4 * C_ND];
+  // barriers: wfull[8] wempty[8] xfull[8] xempty[8] aready[2][NA] afree[2][NA] dready[2][ND] dfree[2][ND] fready[2] ffree[2]
+  __shared__ __align__(8) unsigned long long sh_bars[4 * C_MAX_DEPTH + 4 * C_NA + 4 * C_ND + 4];
   __shared__ uint32_t sh_tmem[3];
-  __shared__ int sh_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int M = p.M, N = p.N, S = p.S, D = p.depth;
-  const long U = p.U, G = gridDim.x;
+  const int M = p.M, N = p.N, S = p.S;
+  const unsigned U = p.U, G = gridDim.x;
   const int u0 = (int)(U * blockIdx.x / G), u1 = (int)(U * (blockIdx.x + 1) / G);
   const int n_units = u1 - u0;
   const unsigned polls = p.wait_polls;
 
+  // shared memory: [weight ring: DW stages][activation ring: DX stages][flush staging: 2 x [16][128] fp32]
   const uint32_t base_u32 = c_smem_u32(c_smem);
   const uint32_t ring = (base_u32 + 127u) & ~127u;
-  const unsigned char *ring_p = c_smem + (ring - base_u32);
+  unsigned char *ring_p = c_smem + (ring - base_u32);
+  const uint32_t xring = ring + C_DW * C_W_BYTES;
+  unsigned char *xring_p = ring_p + C_DW * C_W_BYTES;
+  float *staging = reinterpret_cast<float *>(xring_p + C_DX * C_XSTAGE);
   const uint32_t bars = c_smem_u32(sh_bars);
-  const uint32_t b_full = bars, b_empty = bars + 8 * C_MAX_DEPTH, b_aready = bars + 16 * C_MAX_DEPTH, b_afree = b_aready + 16 * C_NA,
-                 b_dready = b_afree + 16 * C_NA, b_dfree = b_dready + 16 * C_ND;
+  const uint32_t b_wfull = bars, b_wempty = bars + 8 * C_MAX_DEPTH, b_xfull = bars + 16 * C_MAX_DEPTH, b_xempty = bars + 24 * C_MAX_DEPTH,
+                 b_aready = bars + 32 * C_MAX_DEPTH, b_afree = b_aready + 16 * C_NA,
+                 b_dready = b_afree + 16 * C_NA, b_dfree = b_dready + 16 * C_ND, b_fready = b_dfree + 16 * C_ND, b_ffree = b_fready + 16;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C_MAX_DEPTH; ++i) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b_full + 8 * i));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(b_empty + 8 * i), "n"(C_DQ_WARPS + C_DRAIN_WARPS));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b_wfull + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(b_wempty + 8 * i), "n"(C_DQ_WARPS));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b_xfull + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(b_xempty + 8 * i), "n"(C_DRAIN_WARPS));
     }
     for (int i = 0; i < 2 * C_NA; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(b_aready + 8 * i));
@@ -212,6 +254,10 @@ __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __gri
     for (int i = 0; i < 2 * C_ND; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b_dready + 8 * i));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(b_dfree + 8 * i));
+    }
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(b_fready + 8 * i));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b_ffree + 8 * i));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -231,93 +277,141 @@ __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __gri
 
   if (warp == C_PRODUCER_WARP) {
     // ---- TMA ring --------------------------------------------------------------------------------------------
-    auto issue_weights = [&](int i, int slot) {
-      const uint32_t full = b_full + 8 * slot, dst = ring + slot * C_STAGE;
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "n"(C_STAGE) : "memory");
-      const int u = u0 + i, t = u / S, s = u - t * S;
-      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+    int t = u0 / S, s = u0 - t * S;  // tile and stage of the next unit to issue
+    auto issue_weights = [&](int slot) {
+      const uint32_t full = b_wfull + 8 * slot;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "n"(C_W_BYTES) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(ring + slot * C_W_BYTES),
                    "l"(reinterpret_cast<uint64_t>(&tm_w)), "r"(t * TILE_N), "r"(s * 32), "r"(full)
                    : "memory");
-      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst + C_W_BYTES),
+    };
+    auto issue_scales = [&](int slot) {
+      const uint32_t full = b_xfull + 8 * slot;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "n"(C_XSTAGE) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(xring + slot * C_XSTAGE),
                    "l"(reinterpret_cast<uint64_t>(&tm_s)), "r"(t * TILE_N), "r"(s * 2), "r"(full)
                    : "memory");
     };
-    auto issue_slab = [&](int i, int slot) {
-      const int s = (u0 + i) % S;
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(ring + slot * C_STAGE + C_W_BYTES + C_SC_BYTES),
-                   "l"(p.slabs + (size_t)s * C_SLAB), "n"(C_SLAB), "r"(b_full + 8 * slot)
+    auto issue_slab = [&](int slot, int stage) {
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(xring + slot * C_XSTAGE + C_SC_BYTES),
+                   "l"(p.slabs + (size_t)stage * C_SLAB), "n"(C_SLAB), "r"(b_xfull + 8 * slot)
                    : "memory");
     };
-    // first ring fill: weights and scales at once (they never depend on the kernel before), slabs after the wait
-    const int first = n_units < D ? n_units : D;
-    if (lane == 0)
-      for (int i = 0; i < first; ++i) issue_weights(i, i);
-    pdl_wait();
+    auto next_unit = [&]() {
+      if (++s == S) {
+        s = 0;
+        ++t;
+      }
+    };
+    // first ring fills: weights and scales at once (they never depend on the kernel before), slabs after the wait
+    const int t_first = t, s_first = s;
+    const int wfirst = n_units < C_DW ? n_units : C_DW, xfirst = n_units < C_DX ? n_units : C_DX;
     if (lane == 0) {
-      for (int i = 0; i < first; ++i) issue_slab(i, i);
-      for (int i = first; i < n_units; ++i) {
-        const int slot = i % D;
-        if (!c_mbar_wait(b_empty + 8 * slot, ((i / D) - 1) & 1, polls)) {
-          atomicExch(p.status, 600 + slot);  // site 600: a ring stage was never released
-          break;
-        }
-        C_TRACE(4, i, 0);
-        issue_weights(i, slot);
-        issue_slab(i, slot);
+      for (int i = 0; i < xfirst; ++i) {
+        if (i < wfirst) issue_weights(i);
+        issue_scales(i);
+        next_unit();
       }
     }
-  } else if (warp == C_ISSUER_WARP) {
-    // ---- MMA issue -------------------------------------------------------------------------------------------
     pdl_wait();
     if (lane == 0) {
-      bool ok = true;
-      for (int i = 0; i < n_units && ok; ++i) {
-        const int slot = i % D;
-        if (!c_mbar_wait(b_full + 8 * slot, (i / D) & 1, polls)) {
-          atomicExch(p.status, 610 + slot);  // site 610: a ring stage never arrived
+      for (int i = 0, ss = s_first; i < xfirst; ++i) {
+        issue_slab(i, ss);
+        if (++ss == S) ss = 0;
+      }
+      // from here on the weight ring runs C_DX - C_DW units behind the activation ring
+      int wt = t_first, ws = s_first;  // unit of the next weight stage
+      for (int i = 0; i < wfirst; ++i)
+        if (++ws == S) {
+          ws = 0;
+          ++wt;
+        }
+      int wslot = 0, wph = 0, xslot = 0, xph = 0;
+      for (int iw = wfirst, ix = xfirst; iw < n_units; ++iw) {
+        if (!c_mbar_wait(b_wempty + 8 * wslot, wph, polls)) {
+          atomicExch(p.status, 600 + wslot);  // site 600: a weight stage was never released
           break;
         }
-        const uint32_t xs = ring + slot * C_STAGE + C_W_BYTES + C_SC_BYTES;
-        C_TRACE(2, i, 0);
+        {
+          const int tt = t, sv = s;
+          t = wt;
+          s = ws;
+          issue_weights(wslot);
+          t = tt;
+          s = sv;
+        }
+        if (++ws == S) {
+          ws = 0;
+          ++wt;
+        }
+        if (++wslot == C_DW) {
+          wslot = 0;
+          wph ^= 1;
+        }
+        if (ix < n_units) {
+          if (!c_mbar_wait(b_xempty + 8 * xslot, xph, polls)) {
+            atomicExch(p.status, 605 + xslot);  // site 605: an activation stage was never released
+            break;
+          }
+          issue_scales(xslot);
+          issue_slab(xslot, s);
+          next_unit();
+          ++ix;
+          if (++xslot == C_DX) {
+            xslot = 0;
+            xph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == C_ISSUER_WARP || warp == C_ISSUER_WARP + 1) {
+    // ---- MMA issue: one thread per quantisation group of a stage -------------------------------------------------
+    pdl_wait();
+    if (lane == 0) {
+      const int h = warp - C_ISSUER_WARP;
+      int slot = 0, fph = 0, ab = 0, aph = 0, di = 0, dph = 0;
+      for (int i = 0; i < n_units; ++i) {
+        if (!c_mbar_wait(b_xfull + 8 * slot, fph, polls)) {
+          atomicExch(p.status, 610 + slot);  // site 610: an activation stage never arrived
+          break;
+        }
+        if (i >= C_ND && !c_mbar_wait(b_dfree + 8 * (h * C_ND + di), dph ^ 1, polls)) {
+          atomicExch(p.status, 620 + h);  // site 620: an accumulator was never read back
+          break;
+        }
+        const uint64_t db0 = c_desc(xring + slot * C_XSTAGE + C_SC_BYTES + h * 8 * 512, 256, 128);
+        const uint32_t td = tmem_d + (h * C_ND + di) * 16;
+        bool ok = true;
 #pragma unroll
-        for (int h = 0; h < 2 && ok; ++h) {
-          const int db_i = h * C_ND + i % C_ND;
-          if (i >= C_ND && !c_mbar_wait(b_dfree + 8 * db_i, ((i / C_ND) - 1) & 1, polls)) {
-            atomicExch(p.status, 620 + h);  // site 620: an accumulator was never read back
+        for (int kbl = 0; kbl < 2; ++kbl) {
+          if (!c_mbar_wait(b_aready + 8 * (h * C_NA + ab), aph, polls)) {
+            atomicExch(p.status, 630 + h * 2 + kbl);  // site 630: an A block was never written
             ok = false;
             break;
           }
-#pragma unroll
-          for (int kbl = 0; kbl < 2; ++kbl) {
-            const int kb = h * 2 + kbl;
-            const int j = 2 * i + kbl, ab = h * C_NA + j % C_NA;
-            if (!c_mbar_wait(b_aready + 8 * ab, (j / C_NA) & 1, polls)) {
-              atomicExch(p.status, 630 + kb);  // site 630: an A block was never written
-              ok = false;
-              break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (kb == 0) C_TRACE(2, i, 1);
-            if (kb == 1) C_TRACE(2, i, 4);
-            const uint32_t ta = a_addr(ab);
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const uint64_t db = c_desc(xs + (kb * 4 + q4) * 512, 256, 128);
-              const uint32_t enable = (kbl | q4) ? 1u : 0u;
-              asm volatile(
-                  "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                  " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d + db_i * 16),
-                  "r"(ta + q4 * 8), "l"(db), "r"(C_IDESC), "r"(enable), "r"(0u)
-                  : "memory");
-            }
-            if (kb == 0) C_TRACE(2, i, 2);
-            c_commit(b_afree + 8 * ab);
-            if (kb == 0) C_TRACE(2, i, 3);
-            if (kb == 1) C_TRACE(2, i, 5);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t ta = a_addr(h * C_NA + ab);
+          const uint64_t db = db0 + (uint64_t)(kbl * 4 * 32);
+          if (kbl == 0) c_mma<false>(td, ta, db);
+          else c_mma<true>(td, ta, db);
+          c_mma<true>(td, ta + 8, db + 32);
+          c_mma<true>(td, ta + 16, db + 64);
+          c_mma<true>(td, ta + 24, db + 96);
+          c_commit(b_afree + 8 * (h * C_NA + ab));
+          if (++ab == C_NA) {
+            ab = 0;
+            aph ^= 1;
           }
-          if (ok) c_commit(b_dready + 8 * db_i);
-          if (h == 0) C_TRACE(2, i, 6);
-          if (h == 1) C_TRACE(2, i, 7);
+        }
+        if (!ok) break;
+        c_commit(b_dready + 8 * (h * C_ND + di));
+        if (++di == C_ND) {
+          di = 0;
+          dph ^= 1;
+        }
+        if (++slot == C_DX) {
+          slot = 0;
+          fph ^= 1;
         }
       }
     }
@@ -327,31 +421,28 @@ __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __gri
     const int h = warp >> 2, q = warp & 3;
     const int n = q * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    int slot = 0, fph = 0, ab = 0, aph = 0;
     bool ok = true;
     for (int i = 0; i < n_units && ok; ++i) {
-      const int slot = i % D;
-      if (!c_mbar_wait(b_full + 8 * slot, (i / D) & 1, polls)) {
-        if (lane == 0) atomicExch(p.status, 640 + slot);  // site 640
+      if (!c_mbar_wait(b_wfull + 8 * slot, fph, polls)) {
+        if (lane == 0) atomicExch(p.status, 640 + slot);  // site 640: a weight stage never arrived
         break;
       }
-      const uint32_t *wsm = reinterpret_cast<const uint32_t *>(ring_p + (size_t)slot * C_STAGE) + (h * 16) * TILE_N + n;
-      C_TRACE(h, i, 0);
+      const uint32_t *wsm = reinterpret_cast<const uint32_t *>(ring_p + (size_t)slot * C_W_BYTES) + (h * 16) * TILE_N + n;
       uint32_t w[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) w[j] = wsm[j * TILE_N];
       __syncwarp();
-      if (lane == 0) c_mbar_arrive(b_empty + 8 * slot);  // this warp's words are in registers
+      if (lane == 0) c_mbar_arrive(b_wempty + 8 * slot);  // this warp's words are in registers
 #pragma unroll
       for (int kbl = 0; kbl < 2; ++kbl) {
-        const int kb = h * 2 + kbl;
-        const int j = 2 * i + kbl, ab = h * C_NA + j % C_NA;
-        if (j >= C_NA && !c_mbar_wait(b_afree + 8 * ab, ((j / C_NA) - 1) & 1, polls)) {
-          if (lane == 0) atomicExch(p.status, 650 + kb);  // site 650: the MMAs that read an A block never finished
+        if (2 * i + kbl >= C_NA && !c_mbar_wait(b_afree + 8 * (h * C_NA + ab), aph ^ 1, polls)) {
+          if (lane == 0) atomicExch(p.status, 650 + h * 2 + kbl);  // site 650: the MMAs that read an A block never finished
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (q == 0) C_TRACE(h, i, 1 + 3 * kbl);
+        const uint32_t ta = a_addr(h * C_NA + ab) + lane_base;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t r[16];
@@ -364,57 +455,59 @@ __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __gri
             r[4 * j + 3] = v8 & 0x00F000F0u;
           }
           asm volatile(
-              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(a_addr(ab) + lane_base + c * 16),
+              "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(ta + c * 16),
               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
               "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
               : "memory");
         }
-        if (q == 0) C_TRACE(h, i, 2 + 3 * kbl);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (q == 0) C_TRACE(h, i, 3 + 3 * kbl);
         __syncwarp();
-        if (lane == 0) c_mbar_arrive(b_aready + 8 * ab);
+        if (lane == 0) c_mbar_arrive(b_aready + 8 * (h * C_NA + ab));
+        if (++ab == C_NA) {
+          ab = 0;
+          aph ^= 1;
+        }
+      }
+      if (++slot == C_DW) {
+        slot = 0;
+        fph ^= 1;
       }
     }
-  } else {
-    // ---- drain: accumulators -> scaled fp32 sums -> partials / output -------------------------------------------
-    pdl_wait();
+  } else if (warp < C_DQ_WARPS + C_DRAIN_WARPS) {
+    // ---- drain: accumulators -> scaled fp32 sums -> staging for the flush warp ----------------------------------
     const int q = warp & 3;
     const int n = q * 32 + lane;
-    const int dtid = threadIdx.x - C_DQ_WARPS * 32;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     float acc[C_MB];
 #pragma unroll
     for (int m = 0; m < C_MB; ++m) acc[m] = 0.f;
     bool ok = true;
+    int slot = 0, fph = 0, di = 0, dph = 0, fb = 0, fphase = 0, flushes = 0;
+    int s = u0 % S;
     for (int i = 0; i < n_units; ++i) {
-      const int slot = i % D;
-      const unsigned char *st = ring_p + (size_t)slot * C_STAGE;
-      if (ok && !c_mbar_wait(b_full + 8 * slot, (i / D) & 1, polls)) ok = false;
+      const unsigned char *st = xring_p + (size_t)slot * C_XSTAGE;
+      if (ok && !c_mbar_wait(b_xfull + 8 * slot, fph, polls)) ok = false;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int db_i = h * C_ND + i % C_ND;
-        if (ok && !c_mbar_wait(b_dready + 8 * db_i, (i / C_ND) & 1, polls)) {
+        if (ok && !c_mbar_wait(b_dready + 8 * (h * C_ND + di), dph, polls)) {
           if (lane == 0) atomicExch(p.status, 660 + h);  // site 660: a group's MMAs never finished; the result is void
           ok = false;
         }
         if (!ok) continue;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (q == 0) C_TRACE(3, i, 3 * h);
         uint32_t d[16];
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]),
               "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
-            : "r"(tmem_d + lane_base + db_i * 16));
+            : "r"(tmem_d + lane_base + (h * C_ND + di) * 16));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (q == 0) C_TRACE(3, i, 3 * h + 1);
         __syncwarp();
-        if (lane == 0) c_mbar_arrive(b_dfree + 8 * db_i);
-        const float sc = __half2float(reinterpret_cast<const __half *>(st + C_W_BYTES)[h * TILE_N + n]);
-        const float4 *corr = reinterpret_cast<const float4 *>(st + C_W_BYTES + C_SC_BYTES + C_X_BYTES + h * C_MB * 4);
+        if (lane == 0) c_mbar_arrive(b_dfree + 8 * (h * C_ND + di));
+        const float sc = __half2float(reinterpret_cast<const __half *>(st)[h * TILE_N + n]);
+        const float4 *corr = reinterpret_cast<const float4 *>(st + C_SC_BYTES + C_X_BYTES + h * C_MB * 4);
 #pragma unroll
         for (int m4 = 0; m4 < 4; ++m4) {
           const float4 c = corr[m4];
@@ -425,60 +518,128 @@ __global__ void __launch_bounds__(C_THREADS, 2) w4a16_gemv_tc_kernel(const __gri
         }
       }
       __syncwarp();
-      if (lane == 0) c_mbar_arrive(b_empty + 8 * slot);  // scales and corrections read, the stage's MMAs complete
-      if (q == 0) C_TRACE(3, i, 6);
-
-      const int u = u0 + i;
-      if (i == n_units - 1 || (u + 1) % S == 0) {
-        // ---- this CTA's part of tile t is complete ----
-        const int t = u / S;
-        auto lo = [&](long b) { return (long)(U * b / G); };
-        long bf = ((long)t * S * G) / U, bl = (((long)(t + 1) * S - 1) * G) / U;
-        while (bf + 1 < G && lo(bf + 1) <= (long)t * S) ++bf;
-        while (bl + 1 < G && lo(bl + 1) <= (long)(t + 1) * S - 1) ++bl;
-        const int cnt = (int)(bl - bf) + 1, mine = (int)(blockIdx.x - bf);
-        const int col = t * TILE_N + n;
-        bool write_out = true;
-        if (cnt > 1 && !(p.debug & 1)) {
-          float *part = p.partial + ((size_t)t * p.max_cnt + mine) * M * TILE_N + n;
+      if (lane == 0) c_mbar_arrive(b_xempty + 8 * slot);  // scales and corrections read, the stage's MMAs complete
+      if (++di == C_ND) {
+        di = 0;
+        dph ^= 1;
+      }
+      if (++slot == C_DX) {
+        slot = 0;
+        fph ^= 1;
+      }
+      if (++s == S || i == n_units - 1) {
+        // this CTA's part of a tile is complete: hand the sums to the flush warp
+        s = 0;
+        if (flushes >= 2 && ok && !c_mbar_wait(b_ffree + 8 * fb, fphase ^ 1, polls)) {
+          if (lane == 0) atomicExch(p.status, 670 + fb);  // site 670: the flush warp never released a staging buffer
+          ok = false;
+        }
+        float *sg = staging + fb * (C_MB * TILE_N) + n;
 #pragma unroll
-          for (int m = 0; m < C_MB; ++m)
-            if (m < M) __stcg(part + m * TILE_N, acc[m]);
+        for (int m = 0; m < C_MB; ++m) {
+          sg[m * TILE_N] = acc[m] * 16777216.0f;
+          acc[m] = 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) c_mbar_arrive(b_fready + 8 * fb);
+        ++flushes;
+        if (++fb == 2) {
+          fb = 0;
+          fphase ^= 1;
+        }
+      }
+    }
+  } else if (warp == C_FLUSH_WARP) {
+    // ---- flush: partial sums to global memory; the last CTA to arrive at a tile adds them up and writes the output
+    pdl_wait();
+    int fb = 0, fphase = 0;
+    int t = u0 / S;
+    const int t_last = (u1 - 1) / S;
+    for (; n_units > 0 && t <= t_last; ++t) {
+      if (!c_mbar_wait(b_fready + 8 * fb, fphase, polls)) {
+        if (lane == 0) atomicExch(p.status, 680 + fb);  // site 680: sums never arrived
+        break;
+      }
+      int first, cnt;
+      c_tile_parts(U, G, (unsigned)S, (unsigned)t, first, cnt);
+      const int mine = (int)blockIdx.x - first;
+      const float4 *sg = reinterpret_cast<const float4 *>(staging + fb * (C_MB * TILE_N)) + lane;
+      const int col = t * TILE_N + lane * 4;
+      const bool col_ok = col < N;  // N is a multiple of 8: a lane's four columns are inside or outside together
+      auto output = [&](int m, float4 v) {
+        if (EPI == EPI_STORE) {
+          uint2 o;
+          o.x = h22u(__floats2half2_rn(v.x, v.y));
+          o.y = h22u(__floats2half2_rn(v.z, v.w));
+          *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(p.out) + (size_t)m * N + col) = o;
+        } else if (EPI == EPI_STORE_F32) {
+          *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + (size_t)m * N + col) = v;
+        } else {
+          float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + (size_t)m * N + col);
+          float4 r = *o;
+          r.x += __half2float(__float2half_rn(v.x));
+          r.y += __half2float(__float2half_rn(v.y));
+          r.z += __half2float(__float2half_rn(v.z));
+          r.w += __half2float(__float2half_rn(v.w));
+          *o = r;
+        }
+      };
+      if (cnt == 1) {
+        for (int m = 0; m < M; ++m) {
+          const float4 v = sg[m * (TILE_N / 4)];
+          if (col_ok) output(m, v);
+        }
+      } else {
+        float4 *part = reinterpret_cast<float4 *>(p.partial + ((size_t)t * p.max_cnt + mine) * M * TILE_N) + lane;
+#pragma unroll
+        for (int m0 = 0; m0 < C_MB; m0 += 8) {
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = sg[(m0 + j) * (TILE_N / 4)];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (m0 + j < M) __stcg(part + (m0 + j) * (TILE_N / 4), v[j]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) c_mbar_arrive(b_ffree + 8 * fb);
+      if (++fb == 2) {
+        fb = 0;
+        fphase ^= 1;
+      }
+      if (cnt > 1) {
+        __threadfence();
+        __syncwarp();
+        unsigned old = 0;
+        if (lane == 0) {
+          old = atomicAdd(p.counters + t, 1u);
+          if (old == (unsigned)(cnt - 1)) p.counters[t] = 0;  // every part of the tile has arrived: ready for the next launch
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == (unsigned)(cnt - 1)) {
           __threadfence();
-          asm volatile("bar.sync 1, %0;" ::"n"(C_DRAIN_WARPS * 32) : "memory");
-          if (dtid == 0) {
-            const unsigned old = atomicAdd(p.counters + t, 1u);
-            const int last = old == (unsigned)(cnt - 1);
-            if (last) p.counters[t] = 0;  // every part of the tile has arrived: ready for the next launch
-            sh_last = last;
-          }
-          asm volatile("bar.sync 1, %0;" ::"n"(C_DRAIN_WARPS * 32) : "memory");
-          write_out = sh_last != 0;
-          if (write_out) {
-            __threadfence();
-            const float *all = p.partial + (size_t)t * p.max_cnt * M * TILE_N + n;
+          const float4 *all = reinterpret_cast<const float4 *>(p.partial + (size_t)t * p.max_cnt * M * TILE_N) + lane;
+          for (int m0 = 0; m0 < M; m0 += 4) {  // four rows at a time: their loads are in flight together
+            float4 sum[4];
 #pragma unroll
-            for (int m = 0; m < C_MB; ++m)
-              if (m < M) {
-                float s = 0.f;
-                for (int c = 0; c < cnt; ++c) s += __ldcg(all + ((size_t)c * M + m) * TILE_N);
-                acc[m] = s;
+            for (int j = 0; j < 4; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < cnt; ++c) {
+              float4 a[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) a[j] = m0 + j < M ? __ldcg(all + ((size_t)c * M + m0 + j) * (TILE_N / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                sum[j].x += a[j].x;
+                sum[j].y += a[j].y;
+                sum[j].z += a[j].z;
+                sum[j].w += a[j].w;
               }
-          }
-          asm volatile("bar.sync 1, %0;" ::"n"(C_DRAIN_WARPS * 32) : "memory");  // sh_last may be rewritten
-        }
-        if (write_out && col < N) {
-#pragma unroll
-          for (int m = 0; m < C_MB; ++m)
-            if (m < M) {
-              const float s = acc[m] * 16777216.0f;
-              if (EPI == EPI_STORE) reinterpret_cast<__half *>(p.out)[(size_t)m * N + col] = __float2half_rn(s);
-              else if (EPI == EPI_STORE_F32) reinterpret_cast<float *>(p.out)[(size_t)m * N + col] = s;
-              else reinterpret_cast<float *>(p.out)[(size_t)m * N + col] += __half2float(__float2half_rn(s));
             }
-        }
 #pragma unroll
-        for (int m = 0; m < C_MB; ++m) acc[m] = 0.f;
+            for (int j = 0; j < 4; ++j)
+              if (col_ok && m0 + j < M) output(m0 + j, sum[j]);
+          }
+        }
       }
     }
   }
@@ -523,8 +684,6 @@ static int tc_scratch(size_t bytes, void **out) {
   return AB200_OK;
 }
 
-int g_tc_debug = 0;  // investigation switches (option "tc_debug")
-long long *g_tc_trace = nullptr;
 constexpr size_t TC_COUNTER_BYTES = 16 * 1024;  // up to 4096 column tiles
 
 bool gemv_tc_eligible(int dtype, int M, int K, int N, int group) {
@@ -562,17 +721,15 @@ int gemv_tc_dispatch(const void *x, int pro, const __half *norm_w, float eps, co
   long G = 2L * sms;
   if (G > U / 2) G = U / 2;
   if (G < 1) G = 1;
+  if (U * (G + 1) >= (1L << 31)) return AB200_OK;  // the kernel's range arithmetic is 32-bit
   const long upc = U / G;  // smallest range
   const int max_cnt = (int)((S + upc - 2) / upc) + 1;
-  int depth = (g_tc_debug >> 4) ? (g_tc_debug >> 4) : 4;
-  const long upc_max = (U + G - 1) / G;
-  if (depth > upc_max) depth = (int)upc_max;
-  const size_t smem = 128 + (size_t)depth * C_STAGE;
+  const size_t smem = 128 + (size_t)C_DW * C_W_BYTES + (size_t)C_DX * C_XSTAGE + 2 * C_MB * TILE_N * sizeof(float);
 
   const size_t slab_bytes = ((size_t)S * C_SLAB + 255) & ~(size_t)255;
   const size_t part_bytes = (size_t)tiles * max_cnt * M * TILE_N * sizeof(float);
   void *scratch = nullptr;
-  if (int rc = tc_scratch(TC_COUNTER_BYTES + slab_bytes + part_bytes + 8192, &scratch)) return rc;
+  if (int rc = tc_scratch(TC_COUNTER_BYTES + slab_bytes + part_bytes, &scratch)) return rc;
   unsigned char *sb = reinterpret_cast<unsigned char *>(scratch);
 
   TcEncodeFn enc = reinterpret_cast<TcEncodeFn>(tensor_map_encoder());
@@ -605,16 +762,10 @@ int gemv_tc_dispatch(const void *x, int pro, const __half *norm_w, float eps, co
   else e = launch_pdl(gemv_tc_prep_kernel<PRO_SILU_MUL>, dim3(C_MB), dim3(256), 0, s, pp);
   if (e != cudaSuccess) return fail(AB200_ECUDA, "w4a16_gemv (tensor-memory kernel): %s", cudaGetErrorString(e));
   TcGemvParams p{sb + TC_COUNTER_BYTES, out, status, reinterpret_cast<float *>(sb + TC_COUNTER_BYTES + slab_bytes),
-                 reinterpret_cast<unsigned *>(sb), M, N, S, (int)U, depth, max_cnt, 1u << 22, g_tc_debug,
-                 (g_tc_debug & 2) ? reinterpret_cast<long long *>(sb + TC_COUNTER_BYTES + slab_bytes + ((part_bytes + 255) & ~(size_t)255)) : nullptr};
-  g_tc_trace = p.trace;
+                 reinterpret_cast<unsigned *>(sb), M, N, S, (int)U, max_cnt, 1u << 22};
   if (epi == EPI_STORE) return launch_tc<EPI_STORE>(tm_w, tm_s, p, (int)G, smem, s);
   if (epi == EPI_RESIDUAL) return launch_tc<EPI_RESIDUAL>(tm_w, tm_s, p, (int)G, smem, s);
   return launch_tc<EPI_STORE_F32>(tm_w, tm_s, p, (int)G, smem, s);
 }
 
 }  // namespace ab200
-
-extern "C" int ab200_tc_trace(long long *host, int n) {
-  return cudaMemcpy(host, ab200::g_tc_trace, n * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
-}
