@@ -5,7 +5,7 @@
 // M axis larger than the decode path handles.  The dequantised weight fed to the tensor cores is
 // exactly w = RN_fp16(scale * fp16(q - 8)) (IR statement 2), the products accumulate in fp32.
 //
-// CTA tile 256 (M) x 256 (N), K step 64, three shared-memory stages, 512 threads, one CTA per SM.
+// CTA tile 256 (M) x 256 (N), K step 64, three shared-memory stages, 512 + 96 threads, one CTA per SM.
 // The two 128-row halves of the tile have their own fp32 accumulator (2 x 256 TMEM columns) and
 // share every dequantised weight tile, which halves the dequantisation work per flop against a
 // 128-row tile.  All 512 threads fill a stage:
@@ -17,14 +17,17 @@
 //      core matrix (LOP3 + 0x6400 magic, HSUB2/HFMA2 for the zero-point, HMUL2 by the group scale,
 //      PRMT back to natural k order), so no transpose is needed and a quarter-warp writes 128
 //      contiguous bytes.
-// One thread then issues eight `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16,
-// both operands K-major, no swizzle; four K steps x two accumulators) per stage and commits them
-// to the stage's mbarrier; a stage is refilled once the MMAs that read it three iterations ago
-// have completed, so filling overlaps the MMAs of the two stages before.  The issuing thread
-// lives in a 17th warp; producers and issuer meet only through mbarriers (weights ready, x tile
-// landed, MMAs done), there is no block-wide barrier inside the K loop.  The epilogue reads the
-// accumulators with `tcgen05.ld` (row = TMEM lane; the four warps that share a lane quarter split
-// the 512 columns), rounds to fp16 and stores.
+// Per stage eight `tcgen05.mma.cta_group::1.kind::f16` (M128 N256 K16, both operands K-major; four K steps
+// x two accumulators) are issued and committed to the stage's mbarrier; a stage is refilled once the MMAs
+// that read it three iterations ago have completed, so filling overlaps the MMAs of the two stages before.
+// Issuing is not free for the issuing thread (descriptors pass through uniform registers, every wait and
+// commit is a dependent instruction): with one thread doing everything a k tile cost that thread more
+// cycles than the tensor pipe needs for its eight MMAs.  So three single-thread roles live in warps 16-18:
+// the MMAs of accumulator 0, the MMAs of accumulator 1 (each commits on its own; the barriers count two
+// arrivals), and the TMA copies of x, which run up to four k tiles ahead.  Producers and issuers meet only
+// through mbarriers (weights ready, x tile landed, MMAs done), there is no block-wide barrier inside the
+// K loop.  The epilogue reads the accumulators with `tcgen05.ld` (row = TMEM lane; the four warps that
+// share a lane quarter split the 512 columns), rounds to fp16 and stores.
 // Every mbarrier wait is bounded and reports through the status word.
 #include <cuda.h>  // CUtensorMap and its enums (types only)
 
@@ -35,7 +38,7 @@ namespace ab200 {
 constexpr int GM_BM = 256, GM_BN = 256, GM_BK = 64;
 constexpr int GM_HM = 128;                     // rows per accumulator (one MMA's M)
 constexpr int GM_FILL_THREADS = 512;               // 16 warps dequantise weights
-constexpr int GM_THREADS = GM_FILL_THREADS + 32;   // + one warp whose lane 0 issues TMA copies and MMAs
+constexpr int GM_THREADS = GM_FILL_THREADS + 96;   // + three warps whose lane 0 issues: the MMAs of accumulator 0, of accumulator 1, the TMA copies
 constexpr int GM_STAGES = 3;    // stages of dequantised weights
 constexpr int GM_ASTAGES = 4;   // stages of the x tile: one more, so that its TMA copy is issued two k tiles ahead
 constexpr int GM_AH_BYTES = GM_HM * GM_BK * 2;  // 16 KiB: one 128-row half of the x tile (128 rows x 128 B)
@@ -79,6 +82,15 @@ __device__ __forceinline__ uint64_t gm_desc_sw128(uint32_t smem_addr) {
 
 __device__ __forceinline__ bool gm_mbar_wait(uint64_t *bar, unsigned parity) {
   const uint32_t addr = gm_smem_u32(bar);
+  {  // non-blocking probe first: cheaper than try_wait when the phase completed long ago
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (unsigned i = 0; i < GM_WAIT_POLLS; ++i) {
     uint32_t done;
     asm volatile(
@@ -104,12 +116,12 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   if (tid == 0) {
     for (int s = 0; s < GM_STAGES; ++s)
     {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&mma_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(gm_smem_u32(&mma_bar[s])));  // one commit per issuing thread
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gm_smem_u32(&b_full_bar[s])), "r"(GM_FILL_THREADS / 32));
     }
     for (int s = 0; s < GM_ASTAGES; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&full_bar[s])));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(gm_smem_u32(&a_free_bar[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(gm_smem_u32(&a_free_bar[s])));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fail_s = 0;
@@ -205,39 +217,40 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
     __syncwarp();
     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&b_full_bar[s])) : "memory");
   };
-  // Issuer (lane 0 of warp 16): keeps the x ring two k tiles ahead and issues the MMAs of a k tile
-  // as soon as its weights and its x tile are in shared memory.
-  auto issue_step = [&](int kt) {
+  // Issuers (lane 0 of warps 16 and 17, one per accumulator): the MMAs of a k tile as soon as its weights
+  // and its x tile are in shared memory.  Issuing costs the thread tens of cycles per instruction
+  // (descriptors through uniform registers, waits, commits), so the work is split over two threads
+  // and the TMA copies have a thread of their own.
+  auto issue_mmas = [&](int kt, int hm) {
     const int s = kt % GM_STAGES, sA = kt % GM_ASTAGES;
-    if (kt + 2 < ktiles) {  // x tile two k tiles ahead: its stage was last read by the MMAs of kt - 2
-      const int s2 = (kt + 2) % GM_ASTAGES;
-      if (kt + 2 >= GM_ASTAGES && !gm_mbar_wait(&a_free_bar[s2], (((kt + 2) / GM_ASTAGES) - 1) & 1)) {
-        ok = false;
-        fail_s = 1;
-      }
-      issue_a(kt + 2);
-    }
     if (!gm_mbar_wait(&b_full_bar[s], (kt / GM_STAGES) & 1) || !gm_mbar_wait(&full_bar[sA], (kt / GM_ASTAGES) & 1)) {
       ok = false;
       fail_s = 1;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t a_base = gm_smem_u32(gm_smem + sA * GM_A_BYTES), b_base = gm_smem_u32(gm_smem + GM_ASTAGES * GM_A_BYTES + s * GM_B_BYTES);
+    const uint64_t da0 = gm_desc_sw128(gm_smem_u32(gm_smem + sA * GM_A_BYTES) + hm * GM_AH_BYTES);
+    const uint64_t db0 = gm_desc(gm_smem_u32(gm_smem + GM_ASTAGES * GM_A_BYTES + s * GM_B_BYTES), (GM_BN / 8) * 128, 128);
+    const uint32_t acc = tmem_acc + hm * GM_BN;
 #pragma unroll
     for (int kb = 0; kb < GM_BK / 16; ++kb) {
-      const uint64_t db = gm_desc(b_base + kb * 2 * (GM_BN / 8) * 128, (GM_BN / 8) * 128, 128);
-      const uint32_t accumulate = (kt > 0 || kb > 0) ? 1u : 0u;
-#pragma unroll
-      for (int hm = 0; hm < 2; ++hm) {
-        const uint64_t da = gm_desc_sw128(a_base + hm * GM_AH_BYTES + kb * 32);  // 16 k = 32 B further into the swizzled row
+      // 16 k further: 32 B into the swizzled x row, two 16-byte chunks of (BN/8)*128 B into the weight tile
+      const uint64_t da = da0 + (uint64_t)(kb * 2), db = db0 + (uint64_t)(kb * (2 * (GM_BN / 8) * 128 / 16));
+      if (kb == 0) {
+        const uint32_t accumulate = kt > 0 ? 1u : 0u;
         asm volatile(
             "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_acc + hm * GM_BN),
+            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(acc),
             "l"(da), "l"(db), "r"(IDESC), "r"(accumulate), "r"(0u)
+            : "memory");
+      } else {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.eq.u32 p, 0, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%4, %4, %4, %4}, p;\n}\n" ::"r"(acc),
+            "l"(da), "l"(db), "r"(IDESC), "r"(0u)
             : "memory");
       }
     }
-    // arrive on the barriers when every MMA issued so far has completed
+    // arrive on the barriers when every MMA this thread issued so far has completed
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(gm_smem_u32(&a_free_bar[sA])) : "memory");
   };
@@ -252,9 +265,19 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
       if (kt + 2 < ktiles) fill_step(kt + 2, r2);
     }
   } else if (lane == 0) {
-    issue_a(0);
-    if (ktiles > 1) issue_a(1);
-    for (int kt = 0; kt < ktiles; ++kt) issue_step(kt);
+    const int role = warp - GM_FILL_THREADS / 32;
+    if (role < 2) {
+      for (int kt = 0; kt < ktiles; ++kt) issue_mmas(kt, role);
+    } else {
+      // x ring: a stage is refilled as soon as both accumulators' MMAs of four k tiles ago are complete
+      for (int kt = 0; kt < ktiles; ++kt) {
+        if (kt >= GM_ASTAGES && !gm_mbar_wait(&a_free_bar[kt % GM_ASTAGES], ((kt / GM_ASTAGES) - 1) & 1)) {
+          ok = false;
+          fail_s = 1;
+        }
+        issue_a(kt);
+      }
+    }
   }
   // ---- drain: the last commit covers every MMA -----------------------------------------------------
   {
