@@ -139,13 +139,14 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_HM >> 4) << 24);
 
   // ---- per-thread fill roles ---------------------------------------------------------------------------
-  // B: column n0 + tid % 256 (clamped), packed rows bh*4 .. bh*4+3 of the stage's eight
+  // B: column n0 + tid % 256, packed rows bh*4 .. bh*4+3 of the stage's eight.  A column beyond N reads
+  // the last column instead: its accumulator columns are never stored.
   const int bcol = tid & (GM_BN - 1), bh = tid >> 8;
-  int nb = n0 + bcol;
-  const bool nb_ok = nb < N;
-  if (!nb_ok) nb = N - 1;
-  const int32_t *bq = p.qw + nb + (size_t)(bh * 4) * N;  // + row * N
-  const __half *bs = p.scales + nb;                      // + (k / group) * N
+  const int nb = min(n0 + bcol, N - 1);
+  const int32_t *qptr = p.qw + nb + (size_t)(bh * 4) * N;  // the packed words of the next k tile to load
+  const __half *sptr = p.scales + nb;                       // its scale
+  const int tiles_per_group = p.group / GM_BK;
+  int group_count = 0;
   const uint32_t b_off = (uint32_t)((bcol >> 3) * 128 + (bcol & 7) * 16 + bh * 4 * (GM_BN / 8) * 128);  // + j * 4096
   // A: thread 0 asks the TMA unit for the two 64 k x 128 row boxes of k tile kt
   auto issue_a = [&](int kt) {
@@ -161,19 +162,27 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   };
 
   // Three register sets for the packed weights: the global loads of k tile kt+3 are issued while
-  // tile kt is being written to shared memory.
+  // tile kt is being written to shared memory.  Loads are issued in k order, so one running pointer
+  // (and a counter for the scale row) serves all three sets.
   struct FillRegs {
     uint32_t b[4];
     __half s;
   };
-  auto load_regs = [&](int kt, FillRegs &r) {  // global -> registers for k tile kt
-    const int row0 = kt * (GM_BK / 8);
-#pragma unroll
+  auto load_next = [&](FillRegs &r) {  // global -> registers for the next k tile
+    const int32_t *p0 = qptr, *p1 = p0 + N, *p2 = p1 + N, *p3 = p2 + N;
     // volatile asm: the loads must be ISSUED here, three tiles ahead of their use, not sunk to it
-    for (int j = 0; j < 4; ++j) asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[j]) : "l"(bq + (size_t)(row0 + j) * N));
+    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[0]) : "l"(p0));
+    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[1]) : "l"(p1));
+    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[2]) : "l"(p2));
+    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(r.b[3]) : "l"(p3));
     unsigned short sbits;
-    asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(sbits) : "l"(bs + (size_t)((kt * GM_BK) / p.group) * N));
+    asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(sbits) : "l"(sptr));
     r.s = __ushort_as_half(sbits);
+    qptr = p3 + (size_t)5 * N;  // eight packed rows on
+    if (++group_count == tiles_per_group) {
+      group_count = 0;
+      sptr += N;
+    }
   };
 
   const int ktiles = K / GM_BK;
@@ -181,12 +190,11 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   // Producer warps (0-15): per k tile wait until the MMAs that read the stage three tiles ago are
   // done, write the dequantised weights, make them visible to the tensor core and arrive (one
   // arrive per warp) on the stage's "weights ready" barrier.  No block-wide barrier in the loop:
-  // warps drift apart and hide each other's latencies.
-  auto fill_step = [&](int kt, FillRegs &r) {
-    const int s = kt % GM_STAGES;
-    unsigned char *sb = gm_smem + GM_ASTAGES * GM_A_BYTES + s * GM_B_BYTES;
-    if (kt >= GM_STAGES) {
-      if (!gm_mbar_wait(&mma_bar[s], ((kt / GM_STAGES) - 1) & 1)) {
+  // warps drift apart and hide each other's latencies.  `round` = kt / 3; the stage is the call site's.
+  auto fill_step = [&](int stage, int round, bool more, FillRegs &r) {
+    unsigned char *sb = gm_smem + GM_ASTAGES * GM_A_BYTES + stage * GM_B_BYTES;
+    if (round > 0) {
+      if (!gm_mbar_wait(&mma_bar[stage], (round - 1) & 1)) {
         ok = false;
         fail_s = 1;
       }
@@ -203,7 +211,6 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
         o.y = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w, HI, MAGIC)), c16th, cm72), sc2));
         o.z = h22u(__hmul2(__hsub2(u2h2(lop3<0xEA>(w8, LO, MAGIC)), c1032), sc2));
         o.w = h22u(__hmul2(__hfma2(u2h2(lop3<0xEA>(w8, HI, MAGIC)), c16th, cm72), sc2));
-        if (!nb_ok) o = make_uint4(0, 0, 0, 0);
         uint4 n;  // back to natural k order: (k0,k1)(k2,k3)(k4,k5)(k6,k7)
         n.x = __byte_perm(o.x, o.y, 0x5410);
         n.y = __byte_perm(o.z, o.w, 0x5410);
@@ -212,10 +219,10 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
         *reinterpret_cast<uint4 *>(sb + j * (GM_BN / 8) * 128 + b_off) = n;
       }
     }
-    if (kt + 3 < ktiles) load_regs(kt + 3, r);  // this set's next tile: three MMA periods to arrive
+    if (more) load_next(r);  // this set's next tile: three MMA periods to arrive
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
     __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&b_full_bar[s])) : "memory");
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&b_full_bar[stage])) : "memory");
   };
   // Issuers (lane 0 of warps 16 and 17, one per accumulator): the MMAs of a k tile as soon as its weights
   // and its x tile are in shared memory.  Issuing costs the thread tens of cycles per instruction
@@ -256,13 +263,13 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   };
   if (warp < GM_FILL_THREADS / 32) {
     FillRegs r0, r1, r2;
-    load_regs(0, r0);
-    if (ktiles > 1) load_regs(1, r1);
-    if (ktiles > 2) load_regs(2, r2);
-    for (int kt = 0; kt < ktiles; kt += 3) {
-      fill_step(kt, r0);
-      if (kt + 1 < ktiles) fill_step(kt + 1, r1);
-      if (kt + 2 < ktiles) fill_step(kt + 2, r2);
+    load_next(r0);
+    if (ktiles > 1) load_next(r1);
+    if (ktiles > 2) load_next(r2);
+    for (int kt = 0, round = 0; kt < ktiles; kt += 3, ++round) {
+      fill_step(0, round, kt + 3 < ktiles, r0);
+      if (kt + 1 < ktiles) fill_step(1, round, kt + 4 < ktiles, r1);
+      if (kt + 2 < ktiles) fill_step(2, round, kt + 5 < ktiles, r2);
     }
   } else if (lane == 0) {
     const int role = warp - GM_FILL_THREADS / 32;
