@@ -298,41 +298,49 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   __syncthreads();
   if (fail_s && tid == 0) atomicExch(p.status, 200);
 
-  // ---- epilogue: TMEM -> registers -> fp16 -> global.  A warp reads the TMEM lanes of its quarter
-  // (warp % 4); the four warps of a quarter take 128 of the 512 columns each: columns 0-255 are the
-  // accumulator of tile rows 0-127, columns 256-511 that of rows 128-255.
+  // ---- epilogue: TMEM -> registers -> fp16 -> shared memory -> global.  A warp reads the TMEM lanes of its
+  // quarter (warp % 4); the four warps of a quarter take 128 of the 512 columns each: columns 0-255 are the
+  // accumulator of tile rows 0-127, columns 256-511 that of rows 128-255.  A thread holds one row, so storing
+  // from registers would scatter 16-byte pieces over 32 rows per instruction; instead the warp parks its
+  // 32 x 128 sub-tile in the (now idle) stage memory and writes it back out row by row, 256 contiguous bytes
+  // per half-warp.
   if (!fail_s && warp < GM_FILL_THREADS / 32) {
+    constexpr int ROWB = 128 * 2 + 16;  // bytes per parked row: the pad spreads the lanes' 16-byte stores over the banks
     const int q = warp & 3, cg = warp >> 2;
     const int hm = cg >> 1, c_begin = (cg & 1) * 128;
-    const int row = m0 + hm * GM_HM + q * 32 + lane;
+    unsigned char *park = gm_smem + (size_t)warp * (32 * ROWB);
     const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(hm * GM_BN);
-#pragma unroll 1
-    for (int c = c_begin; c < c_begin + 128; c += 16) {
+#pragma unroll 2
+    for (int c = 0; c < 128; c += 16) {
       uint32_t r[16];
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
           : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
             "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-          : "r"(taddr + c));
+          : "r"(taddr + c_begin + c));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < M) {
-        __half *o = p.out + (size_t)row * N + n0 + c;
-        if (n0 + c + 16 <= N) {
-          uint4 h0, h1;
-          h0.x = h22u(__floats2half2_rn(__uint_as_float(r[0]), __uint_as_float(r[1])));
-          h0.y = h22u(__floats2half2_rn(__uint_as_float(r[2]), __uint_as_float(r[3])));
-          h0.z = h22u(__floats2half2_rn(__uint_as_float(r[4]), __uint_as_float(r[5])));
-          h0.w = h22u(__floats2half2_rn(__uint_as_float(r[6]), __uint_as_float(r[7])));
-          h1.x = h22u(__floats2half2_rn(__uint_as_float(r[8]), __uint_as_float(r[9])));
-          h1.y = h22u(__floats2half2_rn(__uint_as_float(r[10]), __uint_as_float(r[11])));
-          h1.z = h22u(__floats2half2_rn(__uint_as_float(r[12]), __uint_as_float(r[13])));
-          h1.w = h22u(__floats2half2_rn(__uint_as_float(r[14]), __uint_as_float(r[15])));
-          *reinterpret_cast<uint4 *>(o) = h0;
-          *reinterpret_cast<uint4 *>(o + 8) = h1;
-        } else {
-          for (int j = 0; j < 16; ++j)
-            if (n0 + c + j < N) o[j] = __float2half_rn(__uint_as_float(r[j]));
-        }
+      uint4 h0, h1;
+      h0.x = h22u(__floats2half2_rn(__uint_as_float(r[0]), __uint_as_float(r[1])));
+      h0.y = h22u(__floats2half2_rn(__uint_as_float(r[2]), __uint_as_float(r[3])));
+      h0.z = h22u(__floats2half2_rn(__uint_as_float(r[4]), __uint_as_float(r[5])));
+      h0.w = h22u(__floats2half2_rn(__uint_as_float(r[6]), __uint_as_float(r[7])));
+      h1.x = h22u(__floats2half2_rn(__uint_as_float(r[8]), __uint_as_float(r[9])));
+      h1.y = h22u(__floats2half2_rn(__uint_as_float(r[10]), __uint_as_float(r[11])));
+      h1.z = h22u(__floats2half2_rn(__uint_as_float(r[12]), __uint_as_float(r[13])));
+      h1.w = h22u(__floats2half2_rn(__uint_as_float(r[14]), __uint_as_float(r[15])));
+      *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2) = h0;
+      *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2 + 16) = h1;
+    }
+    __syncwarp();
+    const int piece = lane & 15;                       // 16-byte piece (8 columns) of a parked row
+    const int col = n0 + c_begin + piece * 8;
+    if (col < N) {                                     // N is a multiple of 8: a piece is inside or outside as a whole
+#pragma unroll 4
+      for (int rr = 0; rr < 32; rr += 2) {
+        const int rl = rr + (lane >> 4);
+        const int row = m0 + hm * GM_HM + q * 32 + rl;
+        const uint4 v = *reinterpret_cast<const uint4 *>(park + rl * ROWB + piece * 16);
+        if (row < M) *reinterpret_cast<uint4 *>(p.out + (size_t)row * N + col) = v;
       }
     }
   }
