@@ -163,8 +163,9 @@ int gemv_tma_dispatch(const void *x, int pro, const __half *norm_w, float eps, c
 
 // TMA ring with the activations streamed through it (w4a16_gemv_slab.cu): batch 5-16
 bool gemv_slab_eligible(int dtype, int M, int K, int N, int group);
+size_t gemv_slab_scratch_bytes(int M, int K);
 int gemv_slab_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
-                       int K, int N, int group, int epi, cudaStream_t s, bool *handled);
+                       int K, int N, int group, int epi, void *scratch, cudaStream_t s, bool *handled);
 
 // tcgen05 variant, weights as the A operand in tensor memory (w4a16_gemv_tc.cu): batch 1-16
 bool gemv_tc_eligible(int dtype, int M, int K, int N, int group);

@@ -643,7 +643,9 @@ static int gemv_f16_impl(const void *x, int pro, const __half *norm_w, float eps
   // rows (gate|up at 16 rows: 20 us against 33) and for the widest at 5-8 rows
   if (impl == 6 || (impl == 0 && ((M >= 9 && N >= 8192) || (M >= 5 && N >= 16384)))) {
     bool handled = false;
-    const int rc = gemv_slab_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, s, &handled);
+    // a caller's workspace holds the slabs behind the persistent kernel's counters (which stay untouched)
+    void *slabs = scratch ? reinterpret_cast<unsigned char *>(scratch) + PERSIST_COUNTER_BYTES : nullptr;
+    const int rc = gemv_slab_dispatch(x, pro, norm_w, eps, qw, scales, out, M, K, N, group, epi, slabs, s, &handled);
     if (rc || handled) return rc;
   }
   if (impl == 4 || (impl == 0 && M >= 2)) {
@@ -728,8 +730,12 @@ extern "C" int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, co
   return gemv_f16(x, PRO_PLAIN, nullptr, 0.f, qweight, scales, out_f32, M, K, N, group, EPI_STORE_F32, nullptr, (cudaStream_t)stream);
 }
 
+static size_t gemv_workspace_bytes(int M, int K, int N) {
+  const size_t a = gemv_persist_scratch_bytes(M, K, N), b = PERSIST_COUNTER_BYTES + gemv_slab_scratch_bytes(M, K);
+  return a > b ? a : b;
+}
 extern "C" size_t ab200_w4a16_gemv_workspace_bytes(int M, int K, int N) {
-  return gemv_persist_scratch_bytes(M, K, N);
+  return gemv_workspace_bytes(M, K, N);
 }
 
 extern "C" int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_f16, float eps, const int32_t *qweight,
@@ -739,8 +745,8 @@ extern "C" int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *n
   if (int rc = check_gemv_args(x, qweight, scales, out, M, K, N, group)) return rc;
   AB200_REQUIRE(prologue >= 0 && prologue <= 2 && epilogue >= 0 && epilogue <= 2, "w4a16_gemv_fused: bad prologue %d / epilogue %d", prologue, epilogue);
   AB200_REQUIRE(prologue != PRO_RMSNORM || norm_weight_f16 != nullptr, "w4a16_gemv_fused: RMSNorm prologue needs a weight vector");
-  AB200_REQUIRE(workspace == nullptr || (aligned16(workspace) && workspace_bytes >= gemv_persist_scratch_bytes(M, K, N)),
-                "w4a16_gemv_fused: workspace must be 16-byte aligned and hold %zu bytes", gemv_persist_scratch_bytes(M, K, N));
+  AB200_REQUIRE(workspace == nullptr || (aligned16(workspace) && workspace_bytes >= gemv_workspace_bytes(M, K, N)),
+                "w4a16_gemv_fused: workspace must be 16-byte aligned and hold %zu bytes", gemv_workspace_bytes(M, K, N));
   return gemv_f16(x, prologue, reinterpret_cast<const __half *>(norm_weight_f16), eps, qweight, scales, out, M, K, N, group, epilogue,
                   workspace, (cudaStream_t)stream);
 }

@@ -427,8 +427,11 @@ static int slab_by_epi(const CUtensorMap &tm_w, const CUtensorMap &tm_s, const S
 }
 
 // Sets *handled when this variant took the call (see gemv_tma_dispatch for the convention).
+size_t gemv_slab_scratch_bytes(int M, int K) { return (size_t)((K + S_STAGE_K - 1) / S_STAGE_K) * slab_bytes(M <= 8 ? 8 : 16); }
+
+// `scratch`: caller's workspace for the slabs (gemv_slab_scratch_bytes), or nullptr for the library-owned buffer.
 int gemv_slab_dispatch(const void *x, int pro, const __half *norm_w, float eps, const int32_t *qw, const void *scales, void *out, int M,
-                       int K, int N, int group, int epi, cudaStream_t s, bool *handled) {
+                       int K, int N, int group, int epi, void *scratch, cudaStream_t s, bool *handled) {
   *handled = false;
   if (!gemv_slab_eligible(AB200_F16, M, K, N, group)) return AB200_OK;
   const int MB = M <= 8 ? 8 : 16;
@@ -454,8 +457,10 @@ int gemv_slab_dispatch(const void *x, int pro, const __half *norm_w, float eps, 
   if ((size_t)depth * stage_pad < (size_t)2 * M * TILE_N * sizeof(float)) return AB200_OK;  // `red` reuses the ring
   const size_t smem = fixed + (size_t)depth * stage_pad;
 
-  void *slabs = nullptr;
-  if (int rc = slab_scratch((size_t)stages * slab, &slabs)) return rc;
+  void *slabs = scratch;
+  if (!slabs) {
+    if (int rc = slab_scratch((size_t)stages * slab, &slabs)) return rc;
+  }
   SlabEncodeFn enc = reinterpret_cast<SlabEncodeFn>(tensor_map_encoder());
   CUtensorMap tm_w, tm_s;
   {

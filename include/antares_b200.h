@@ -115,9 +115,12 @@ int ab200_w4a16_gemv_f32out(const void *x, const int32_t *qweight, const void *s
  * workspace: device scratch of at least ab200_w4a16_gemv_workspace_bytes(M, K, N) bytes, 16-byte
  * aligned, whose first 64 KiB are zero before the first use (the kernel leaves them zero); NULL =
  * use the library's own per-device scratch.  Calls sharing a workspace must not overlap on the
- * GPU.  The library scratch is allocated (cudaMalloc + a device synchronise) by the first call
+ * GPU.  Two kernels use scratch: the persistent kernel (option gemv_impl=3) and the kernel that
+ * streams the activations through the TMA ring (the default for 9-16 rows at N >= 8192 and for
+ * 5-8 rows at N >= 16384, which stages the re-ordered activations there).  The library scratch is
+ * allocated (cudaMalloc, for the persistent kernel also a device synchronise) by the first call
  * that needs it on a device, also from ab200_w4a16_gemv / _residual / _f32out: make that first
- * call outside stream capture. */
+ * call outside stream capture, and do not let two such calls overlap on different streams. */
 int ab200_w4a16_gemv_fused(const void *x, int prologue, const void *norm_weight_f16, float eps,
                            const int32_t *qweight, const void *scales, void *out, int epilogue,
                            int M, int K, int N, int group, void *workspace, size_t workspace_bytes,

@@ -206,7 +206,10 @@ def test_streamed_activation_gemv_matches_oracle(cuda, impl, M, K, N):
         y = ops.w4a16_gemv(_dev(x16, cuda), dq, ds)
         y2 = ops.w4a16_gemv(_dev(x16, cuda), dq, ds)
         yn = torch.empty((M, N), dtype=torch.float16, device=cuda)
-        ops.w4a16_gemv_fused(_dev(x32, cuda), dq, ds, yn, prologue=ops.PRO_RMSNORM, norm_weight=_dev(wn, cuda), eps=1e-6)
+        # a caller's workspace holds the staged activations behind its first 64 KiB (which stay zero)
+        ws = torch.zeros(ops.gemv_workspace_bytes(M, K, N), dtype=torch.uint8, device=cuda)
+        ops.w4a16_gemv_fused(_dev(x32, cuda), dq, ds, yn, prologue=ops.PRO_RMSNORM, norm_weight=_dev(wn, cuda), eps=1e-6, workspace=ws)
+        assert torch.count_nonzero(ws[:65536]) == 0
         resid = _dev(resid0, cuda)
         ops.w4a16_gemv_fused(_dev(gu, cuda), dq, ds, resid, prologue=ops.PRO_SILU_MUL, epilogue=ops.EPI_RESIDUAL)
         torch.cuda.synchronize()
