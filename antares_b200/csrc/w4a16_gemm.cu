@@ -273,7 +273,16 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
     }
   } else if (lane == 0) {
     const int role = warp - GM_FILL_THREADS / 32;
-    if (role < 2) {
+    if (role < 2 && m0 + role * GM_HM >= M) {
+      // this accumulator's rows lie beyond M (a prompt of at most 128 rows): nothing to multiply; arrive in
+      // step with the other issuing thread so that the stage barriers still count two arrivals per use
+      for (int kt = 0; kt < ktiles; ++kt) {
+        const int s = kt % GM_STAGES, sA = kt % GM_ASTAGES;
+        if (!gm_mbar_wait(&b_full_bar[s], (kt / GM_STAGES) & 1) || !gm_mbar_wait(&full_bar[sA], (kt / GM_ASTAGES) & 1)) fail_s = 1;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&mma_bar[s])) : "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gm_smem_u32(&a_free_bar[sA])) : "memory");
+      }
+    } else if (role < 2) {
       for (int kt = 0; kt < ktiles; ++kt) issue_mmas(kt, role);
     } else {
       // x ring: a stage is refilled as soon as both accumulators' MMAs of four k tiles ago are complete
@@ -309,6 +318,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
     const int q = warp & 3, cg = warp >> 2;
     const int hm = cg >> 1, c_begin = (cg & 1) * 128;
     unsigned char *park = gm_smem + (size_t)warp * (32 * ROWB);
+    if (m0 + hm * GM_HM + q * 32 < M) {  // a warp whose 32 rows all lie beyond M has nothing to store
     const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(hm * GM_BN);
 #pragma unroll 2
     for (int c = 0; c < 128; c += 16) {
@@ -342,6 +352,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
         const uint4 v = *reinterpret_cast<const uint4 *>(park + rl * ROWB + piece * 16);
         if (row < M) *reinterpret_cast<uint4 *>(p.out + (size_t)row * N + col) = v;
       }
+    }
     }
   }
   (void)ok;

@@ -193,6 +193,7 @@ class LlamaInt4Decoder:
         self.launches_per_step = 0
         self._steps_left = 0   # host count of steps the cache and the token log still have room for
         self.gemv_impl_by_shape = {}
+        self._prefill_graphs = {}  # prompt length -> (CUDA graph of the batched prompt pass, its buffers)
         self.prefetch = int(prefetch)   # 1: every projection kernel also pulls the next one's weights into L2
         self._plist = []
         for w in self.layers:
@@ -296,13 +297,41 @@ class LlamaInt4Decoder:
         prompt = np.asarray(prompt, np.int32)
         T = int(len(prompt))
         assert 1 <= T <= cfg.max_seq and T <= self.max_tokens
-        dev, st = self.dev, torch.cuda.current_stream().cuda_stream
-        self.reset(torch.from_numpy(prompt).to(dev))
+        self.reset(torch.from_numpy(prompt).to(self.dev))
+        cached = self._prefill_graphs.get(T)
+        if cached is None:
+            # first prompt of this length: run the pass eagerly, then record it as a CUDA graph over the same
+            # buffers (352 launches at 32 layers: replayed, the pass is bound by the GPU, not by the host)
+            bufs = self._prefill_buffers(T)
+            self._prefill_pass(T, bufs)
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    self._prefill_pass(T, bufs)
+            torch.cuda.current_stream().wait_stream(side)
+            if len(self._prefill_graphs) >= 4:  # a few prompt lengths at most stay recorded
+                self._prefill_graphs.pop(next(iter(self._prefill_graphs)))
+            self._prefill_graphs[T] = (graph, bufs)
+        else:
+            cached[0].replay()
+        self._steps_left = min(cfg.max_seq, self.max_tokens) - T
+        return int(self.token.item())
+
+    def _prefill_buffers(self, T):
+        d, f, dev = self.cfg.dim, self.fl, self.dev
+        h16 = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)
+        return dict(x=torch.empty(T, d, dtype=torch.float32, device=dev), xb=h16(T, d), vqk=h16(T, 3 * d), q=h16(T, d), att=h16(T, d),
+                    o=h16(T, d), gu=h16(T, 2 * f), hh=h16(T, f))
+
+    def _prefill_pass(self, T, b):
+        """The launches of one batched prompt pass on torch's current stream; reads self.prompt[:T], pos = 0."""
+        cfg = self.cfg
+        st = torch.cuda.current_stream().cuda_stream
         toks = self.prompt[:T]
         d, f = cfg.dim, self.fl
-        h16 = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)
-        x = torch.empty(T, d, dtype=torch.float32, device=dev)
-        xb, vqk, q, att, o, gu, hh = h16(T, d), h16(T, 3 * d), h16(T, d), h16(T, d), h16(T, d), h16(T, 2 * f), h16(T, f)
+        x, xb, vqk, q, att, o, gu, hh = b["x"], b["xb"], b["vqk"], b["q"], b["att"], b["o"], b["gu"], b["hh"]
         call("ab200_embed_rows", self.embed.data_ptr(), toks.data_ptr(), x.data_ptr(), T, d, cfg.vocab, st)
 
         def gemm(a, l, k, out):
@@ -330,9 +359,7 @@ class LlamaInt4Decoder:
         call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), d, self.vl, st)
         call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), T, self.token.data_ptr(), self.pos.data_ptr(),
              self.out_tokens.data_ptr(), self.out_tokens.numel(), st)
-        self._steps_left = min(cfg.max_seq, self.max_tokens) - T
         self.out_tokens[:T].copy_(toks)
-        return int(self.token.item())
 
     # -- graph ---------------------------------------------------------------------------------------
     def capture(self, n_prompt):

@@ -93,6 +93,13 @@ def test_batched_prefill_matches_token_by_token(cuda):
     lg = c.logits.cpu().numpy()
     assert np.abs(lg - ref_logits[7]).max() <= TOL * np.abs(ref_logits[7]).max()
     assert int(c.token.item()) == int(ref_tokens[8])
+    # a second prompt of the same length replays the recorded pass: same result as a fresh decoder's first pass
+    other = synth_prompt(cfg, 8, 5)
+    first_tok, first_logits = c.prefill(other), c.logits.clone()
+    c.prefill(prompt[:8])
+    assert torch.equal(c.logits, torch.from_numpy(lg).to(cuda))
+    fresh = LlamaInt4Decoder(cfg, cuda)
+    assert fresh.prefill(other) == first_tok and torch.equal(fresh.logits, first_logits)
     assert ops.kernel_status() == 0
 
 
