@@ -53,6 +53,9 @@ struct GemmParams {
   __half *out;
   int M, K, N, group;
   int *status;
+  int parts;           // K ranges per tile: > 1 when there are too few tiles to fill the GPU
+  float *partial;      // [tiles][parts][16 column chunks][256 rows][16] fp32: K-split partial accumulators
+  unsigned *counters;  // [tiles], zero between launches
 };
 
 __device__ __forceinline__ uint32_t gm_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -103,15 +106,20 @@ __device__ __forceinline__ bool gm_mbar_wait(uint64_t *bar, unsigned parity) {
   return false;
 }
 
+// SPLIT: the grid's z dimension splits K (few tiles); the unsplit instantiation carries none of that code.
+template <bool SPLIT>
 __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, GemmParams p) {
   extern __shared__ __align__(1024) unsigned char gm_smem_raw[];
   unsigned char *gm_smem = gm_smem_raw + ((1024u - (gm_smem_u32(gm_smem_raw) & 1023u)) & 1023u);  // swizzle atoms need 1024-B alignment
   __shared__ __align__(8) uint64_t mma_bar[GM_STAGES], b_full_bar[GM_STAGES], full_bar[GM_ASTAGES], a_free_bar[GM_ASTAGES];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int fail_s;
+  __shared__ int fail_s, last_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * GM_BN;
   const int K = p.K, N = p.N, M = p.M;
+  // K range of this CTA, in k tiles of 64: [kt0, kt0 + ktiles)
+  const int kt0 = SPLIT ? (K / GM_BK) * (int)blockIdx.z / p.parts : 0;
+  const int ktiles = SPLIT ? (K / GM_BK) * ((int)blockIdx.z + 1) / p.parts - kt0 : K / GM_BK;
 
   if (tid == 0) {
     for (int s = 0; s < GM_STAGES; ++s)
@@ -143,10 +151,10 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   // the last column instead: its accumulator columns are never stored.
   const int bcol = tid & (GM_BN - 1), bh = tid >> 8;
   const int nb = min(n0 + bcol, N - 1);
-  const int32_t *qptr = p.qw + nb + (size_t)(bh * 4) * N;  // the packed words of the next k tile to load
-  const __half *sptr = p.scales + nb;                       // its scale
   const int tiles_per_group = p.group / GM_BK;
-  int group_count = 0;
+  const int32_t *qptr = p.qw + nb + (size_t)(kt0 * 8 + bh * 4) * N;  // the packed words of the next k tile to load
+  const __half *sptr = p.scales + nb + (size_t)(kt0 / tiles_per_group) * N;  // its scale
+  int group_count = kt0 % tiles_per_group;
   const uint32_t b_off = (uint32_t)((bcol >> 3) * 128 + (bcol & 7) * 16 + bh * 4 * (GM_BN / 8) * 128);  // + j * 4096
   // A: thread 0 asks the TMA unit for the two 64 k x 128 row boxes of k tile kt
   auto issue_a = [&](int kt) {
@@ -157,7 +165,7 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
 #pragma unroll
     for (int hm = 0; hm < 2; ++hm)
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst + hm * GM_AH_BYTES),
-                   "l"(reinterpret_cast<uint64_t>(&tm_x)), "r"(kt * GM_BK), "r"(m0 + hm * GM_HM), "r"(bar)
+                   "l"(reinterpret_cast<uint64_t>(&tm_x)), "r"((kt0 + kt) * GM_BK), "r"(m0 + hm * GM_HM), "r"(bar)
                    : "memory");
   };
 
@@ -185,7 +193,6 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
     }
   };
 
-  const int ktiles = K / GM_BK;
   bool ok = true;
   // Producer warps (0-15): per k tile wait until the MMAs that read the stage three tiles ago are
   // done, write the dequantised weights, make them visible to the tensor core and arrive (one
@@ -313,52 +320,141 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   // from registers would scatter 16-byte pieces over 32 rows per instruction; instead the warp parks its
   // 32 x 128 sub-tile in the (now idle) stage memory and writes it back out row by row, 256 contiguous bytes
   // per half-warp.
-  if (!fail_s && warp < GM_FILL_THREADS / 32) {
+  // With a K split (few tiles, p.parts > 1) every CTA first stores its fp32 accumulators as partial sums; the
+  // last CTA of a tile to arrive adds the parts in part order (bitwise repeatable) and runs the epilogue.
+  if (warp < GM_FILL_THREADS / 32) {
     constexpr int ROWB = 128 * 2 + 16;  // bytes per parked row: the pad spreads the lanes' 16-byte stores over the banks
     const int q = warp & 3, cg = warp >> 2;
     const int hm = cg >> 1, c_begin = (cg & 1) * 128;
     unsigned char *park = gm_smem + (size_t)warp * (32 * ROWB);
-    if (m0 + hm * GM_HM + q * 32 < M) {  // a warp whose 32 rows all lie beyond M has nothing to store
+    const bool rows_live = !fail_s && m0 + hm * GM_HM + q * 32 < M;  // a warp whose 32 rows all lie beyond M has nothing to store
     const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(hm * GM_BN);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    // partial sums: [tile][part][16-column chunk][256 rows][16] fp32: a warp's 32 rows of one chunk are 2 KiB of consecutive addresses
+    float *mine = SPLIT ? p.partial + ((size_t)tile_id * p.parts + blockIdx.z) * (GM_BM * GM_BN) + (size_t)(hm * GM_HM + q * 32 + lane) * 16 : nullptr;
+    bool finish = true;
+    if (SPLIT) {
+      if (rows_live) {
 #pragma unroll 2
-    for (int c = 0; c < 128; c += 16) {
-      uint32_t r[16];
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-            "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-          : "r"(taddr + c_begin + c));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      uint4 h0, h1;
-      h0.x = h22u(__floats2half2_rn(__uint_as_float(r[0]), __uint_as_float(r[1])));
-      h0.y = h22u(__floats2half2_rn(__uint_as_float(r[2]), __uint_as_float(r[3])));
-      h0.z = h22u(__floats2half2_rn(__uint_as_float(r[4]), __uint_as_float(r[5])));
-      h0.w = h22u(__floats2half2_rn(__uint_as_float(r[6]), __uint_as_float(r[7])));
-      h1.x = h22u(__floats2half2_rn(__uint_as_float(r[8]), __uint_as_float(r[9])));
-      h1.y = h22u(__floats2half2_rn(__uint_as_float(r[10]), __uint_as_float(r[11])));
-      h1.z = h22u(__floats2half2_rn(__uint_as_float(r[12]), __uint_as_float(r[13])));
-      h1.w = h22u(__floats2half2_rn(__uint_as_float(r[14]), __uint_as_float(r[15])));
-      *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2) = h0;
-      *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2 + 16) = h1;
-    }
-    __syncwarp();
-    const int piece = lane & 15;                       // 16-byte piece (8 columns) of a parked row
-    const int col = n0 + c_begin + piece * 8;
-    if (col < N) {                                     // N is a multiple of 8: a piece is inside or outside as a whole
-#pragma unroll 4
-      for (int rr = 0; rr < 32; rr += 2) {
-        const int rl = rr + (lane >> 4);
-        const int row = m0 + hm * GM_HM + q * 32 + rl;
-        const uint4 v = *reinterpret_cast<const uint4 *>(park + rl * ROWB + piece * 16);
-        if (row < M) *reinterpret_cast<uint4 *>(p.out + (size_t)row * N + col) = v;
+        for (int c = 0; c < 128; c += 16) {
+          uint32_t r[16];
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(taddr + c_begin + c));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          float4 *dst = reinterpret_cast<float4 *>(mine + (size_t)((c_begin + c) / 16) * (GM_BM * 16));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+        }
       }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(GM_FILL_THREADS) : "memory");
+      if (tid == 0) {
+        const unsigned old = atomicAdd(p.counters + tile_id, 1u);
+        const int last = old == (unsigned)(p.parts - 1);
+        if (last) p.counters[tile_id] = 0;  // ready for the next launch
+        last_s = last;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(GM_FILL_THREADS) : "memory");
+      finish = last_s != 0;
+      if (finish) __threadfence();
     }
+    if (finish && rows_live) {
+      const float *all = SPLIT ? p.partial + (size_t)tile_id * p.parts * (GM_BM * GM_BN) + (size_t)(hm * GM_HM + q * 32 + lane) * 16 : nullptr;
+#pragma unroll 2
+      for (int c = 0; c < 128; c += 16) {
+        float v[16];
+        if (SPLIT) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int pt0 = 0; pt0 < p.parts; pt0 += 4) {  // four parts' loads in flight together, added in part order
+            float4 a[4][4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+              const float4 *src = reinterpret_cast<const float4 *>(all + (size_t)(pt0 + pp) * (GM_BM * GM_BN) + (size_t)((c_begin + c) / 16) * (GM_BM * 16));
+#pragma unroll
+              for (int j = 0; j < 4; ++j) a[pp][j] = pt0 + pp < p.parts ? __ldcg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[4 * j] += a[pp][j].x;
+                v[4 * j + 1] += a[pp][j].y;
+                v[4 * j + 2] += a[pp][j].z;
+                v[4 * j + 3] += a[pp][j].w;
+              }
+          }
+        } else {
+          uint32_t r[16];
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(taddr + c_begin + c));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        uint4 h0, h1;
+        h0.x = h22u(__floats2half2_rn(v[0], v[1]));
+        h0.y = h22u(__floats2half2_rn(v[2], v[3]));
+        h0.z = h22u(__floats2half2_rn(v[4], v[5]));
+        h0.w = h22u(__floats2half2_rn(v[6], v[7]));
+        h1.x = h22u(__floats2half2_rn(v[8], v[9]));
+        h1.y = h22u(__floats2half2_rn(v[10], v[11]));
+        h1.z = h22u(__floats2half2_rn(v[12], v[13]));
+        h1.w = h22u(__floats2half2_rn(v[14], v[15]));
+        *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2) = h0;
+        *reinterpret_cast<uint4 *>(park + lane * ROWB + c * 2 + 16) = h1;
+      }
+      __syncwarp();
+      const int piece = lane & 15;                       // 16-byte piece (8 columns) of a parked row
+      const int col = n0 + c_begin + piece * 8;
+      if (col < N) {                                     // N is a multiple of 8: a piece is inside or outside as a whole
+#pragma unroll 4
+        for (int rr = 0; rr < 32; rr += 2) {
+          const int rl = rr + (lane >> 4);
+          const int row = m0 + hm * GM_HM + q * 32 + rl;
+          const uint4 v = *reinterpret_cast<const uint4 *>(park + rl * ROWB + piece * 16);
+          if (row < M) *reinterpret_cast<uint4 *>(p.out + (size_t)row * N + col) = v;
+        }
+      }
     }
   }
   (void)ok;
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * GM_BN) : "memory");
+}
+
+// Library-owned scratch for K-split launches, one per device: [counters, zero between launches][partial sums].
+// Allocated (counters zeroed) by the first call that needs it, grown when a larger problem arrives; at most one
+// 256 x 256 fp32 tile per SM (37 MiB on 148 SMs).
+constexpr size_t GEMM_COUNTER_BYTES = 1024;
+static void *g_gemm_scratch[64] = {nullptr};
+static size_t g_gemm_scratch_bytes[64] = {0};
+static int gemm_scratch(size_t bytes, void **out) {
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
+  if (g_gemm_scratch_bytes[dev] < bytes) {
+    if (g_gemm_scratch[dev]) {
+      AB200_CUDA(cudaDeviceSynchronize());
+      AB200_CUDA(cudaFree(g_gemm_scratch[dev]));
+      g_gemm_scratch[dev] = nullptr;
+      g_gemm_scratch_bytes[dev] = 0;
+    }
+    AB200_CUDA(cudaMalloc(&g_gemm_scratch[dev], bytes));
+    AB200_CUDA(cudaMemset(g_gemm_scratch[dev], 0, GEMM_COUNTER_BYTES));
+    AB200_CUDA(cudaDeviceSynchronize());
+    g_gemm_scratch_bytes[dev] = bytes;
+  }
+  *out = g_gemm_scratch[dev];
+  return AB200_OK;
 }
 
 }  // namespace ab200
@@ -376,7 +472,20 @@ extern "C" int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const voi
   AB200_REQUIRE(aligned16(x) && aligned16(qweight) && aligned16(scales) && aligned16(out), "w4a16_gemm: pointers must be 16-byte aligned");
   int *status = kernel_error_ptr();
   AB200_REQUIRE(status != nullptr, "w4a16_gemm: cannot resolve the status word");
-  GemmParams p{(const __half *)x, qweight, (const __half *)scales, (__half *)out, M, K, N, group, status};
+  // Few tiles (a short prompt): split K over the idle SMs, at most 4 ranges (the last CTA of a tile adds all
+  // parts, one batch of loads per 16 columns) of at least 8 k tiles each
+  const int tiles = ((N + GM_BN - 1) / GM_BN) * ((M + GM_BM - 1) / GM_BM), G = sm_count();
+  int parts = G / tiles;
+  if (parts > 4) parts = 4;
+  if (parts > (K / GM_BK) / 8) parts = (K / GM_BK) / 8;
+  if (parts < 1) parts = 1;
+  void *scratch = nullptr;
+  if (parts > 1) {
+    if (int rc = gemm_scratch(GEMM_COUNTER_BYTES + (size_t)tiles * parts * GM_BM * GM_BN * sizeof(float), &scratch)) return rc;
+  }
+  GemmParams p{(const __half *)x, qweight, (const __half *)scales, (__half *)out, M, K, N, group, status, parts,
+               scratch ? reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(scratch) + GEMM_COUNTER_BYTES) : nullptr,
+               reinterpret_cast<unsigned *>(scratch)};
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                CUtensorMapFloatOOBfill);
@@ -392,9 +501,11 @@ extern "C" int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const voi
     if (r != CUDA_SUCCESS) return fail(AB200_ECUDA, "w4a16_gemm: cuTensorMapEncodeTiled(x) failed with %d", (int)r);
   }
   const size_t smem = (size_t)GM_ASTAGES * GM_A_BYTES + (size_t)GM_STAGES * GM_B_BYTES + 1024;
-  AB200_CUDA(cudaFuncSetAttribute(w4a16_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const dim3 grid((N + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM);
-  w4a16_gemm_tcgen05_kernel<<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(tm_x, p);
+  AB200_CUDA(cudaFuncSetAttribute(w4a16_gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  AB200_CUDA(cudaFuncSetAttribute(w4a16_gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const dim3 grid((N + GM_BN - 1) / GM_BN, (M + GM_BM - 1) / GM_BM, parts);
+  if (parts > 1) w4a16_gemm_tcgen05_kernel<true><<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(tm_x, p);
+  else w4a16_gemm_tcgen05_kernel<false><<<grid, GM_THREADS, smem, (cudaStream_t)stream>>>(tm_x, p);
   AB200_CHECK_LAUNCH("w4a16_gemm");
   return AB200_OK;
 }
