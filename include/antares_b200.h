@@ -163,8 +163,13 @@ int ab200_w4a16_gemv_static(const void *x, const int32_t *qweight, const void *s
  * all-reduced partial. */
 int ab200_residual_add(float *x_f32, const float *partial_f32, int n, void *stream);
 
-/* Prefill contraction on tensor cores (tcgen05 + TMEM): same arithmetic, M a multiple of 128.
- * Replaces the same exported op called with a leading M axis. */
+/* Prefill contraction on tensor cores (tcgen05 + TMEM): same arithmetic, any M >= 1 (fp16, K a
+ * multiple of 64, group a multiple of 64 dividing K, N a multiple of 8).  Replaces the same
+ * exported op called with a leading M axis.  When the problem has fewer 256 x 256 output tiles
+ * than half the SMs, K is split over the idle SMs and the partial sums pass through a
+ * library-owned per-device scratch (at most 37 MiB), allocated by the first such call on a
+ * device: make that call outside stream capture, and do not let two such calls overlap on
+ * different streams. */
 int ab200_w4a16_gemm(const void *x, const int32_t *qweight, const void *scales, void *out, int M,
                      int K, int N, int group, int dtype, void *stream);
 
