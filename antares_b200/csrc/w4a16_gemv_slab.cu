@@ -134,6 +134,15 @@ struct SlabGemvParams {
 __device__ __forceinline__ uint32_t s_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ bool s_mbar_wait(uint32_t bar, unsigned parity, unsigned polls) {
+  {  // non-blocking probe first: cheaper than try_wait when the phase has already completed
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (unsigned i = 0; i < polls; ++i) {
     uint32_t done;
     asm volatile(
