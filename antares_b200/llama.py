@@ -187,6 +187,7 @@ class LlamaInt4Decoder:
         self.n_prompt = 0
         self.att_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graph = None
+        self.graph_io = None
         self._ref_cache = {}
         self.tiled = bool(tiled)
         self.fused_allreduce = bool(fused_allreduce)  # tensor parallel: sum over ranks inside the O / down projection kernels
@@ -376,6 +377,13 @@ class LlamaInt4Decoder:
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=side):
                 self.step_eager()
+            # the same step between the copy of a host token id in and the copy of the chosen id out
+            # (pinned host buffers), for step(): one launch per token instead of three stream operations
+            self.graph_io = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph_io, stream=side):
+                self.token.copy_(self._pin_in, non_blocking=True)
+                self.step_eager()
+                self._pin_out.copy_(self.token, non_blocking=True)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         return self
@@ -425,9 +433,7 @@ class LlamaInt4Decoder:
             raise IndexError("step(): the sequence has reached max_seq=%d / max_tokens=%d; reset() first" % (self.cfg.max_seq, self.max_tokens))
         self._steps_left -= 1
         self._pin_in[0] = int(token)
-        self.token.copy_(self._pin_in, non_blocking=True)
-        self.graph.replay()
-        self._pin_out.copy_(self.token, non_blocking=True)
+        self.graph_io.replay()
         torch.cuda.current_stream().synchronize()
         return int(self._pin_out[0])
 
