@@ -21,6 +21,31 @@ int fail(int code, const char *fmt, ...) {
 
 void clear_error() { g_err[0] = 0; }
 
+static void *g_lib_buf[LIB_BUF_COUNT][64] = {};
+static size_t g_lib_buf_bytes[LIB_BUF_COUNT][64] = {};
+int library_buffer(int which, size_t bytes, size_t min_bytes, size_t zero_bytes, void **out) {
+  int dev = 0;
+  AB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || which < 0 || which >= LIB_BUF_COUNT) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
+  void *&buf = g_lib_buf[which][dev];
+  size_t &have = g_lib_buf_bytes[which][dev];
+  if (have < bytes) {
+    const size_t want = bytes < min_bytes ? min_bytes : bytes;
+    if (buf) {
+      AB200_CUDA(cudaDeviceSynchronize());
+      AB200_CUDA(cudaFree(buf));
+      buf = nullptr;
+      have = 0;
+    }
+    AB200_CUDA(cudaMalloc(&buf, want));
+    if (zero_bytes) AB200_CUDA(cudaMemset(buf, 0, zero_bytes < want ? zero_bytes : want));
+    AB200_CUDA(cudaDeviceSynchronize());
+    have = want;
+  }
+  *out = buf;
+  return AB200_OK;
+}
+
 int *kernel_error_ptr() {
   static int *cached[64] = {nullptr};
   int dev = 0;

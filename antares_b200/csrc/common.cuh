@@ -36,6 +36,12 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 int sm_count();  // SMs of the current device (cached per device)
 void *tensor_map_encoder();  // cuTensorMapEncodeTiled through the runtime's driver entry point query, or nullptr
 int *kernel_error_ptr();  // device address of the status word that ab200_kernel_status reads (nullptr on failure)
+// Library-owned device buffers, one per user and device: at least `bytes` long (never shorter than min_bytes),
+// the first zero_bytes of it zeroed whenever it is allocated or grown (which also synchronises the device).
+// Callers keep what they need zero between launches themselves.  Not for use under stream capture before
+// the first call; two kernels that use the same buffer must not overlap on the GPU.
+enum { LIB_BUF_PERSIST = 0, LIB_BUF_SLABS, LIB_BUF_TC, LIB_BUF_GEMM, LIB_BUF_COUNT };
+int library_buffer(int which, size_t bytes, size_t min_bytes, size_t zero_bytes, void **out);
 
 // Programmatic dependent launch: when enabled (option "pdl"), kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization, so a kernel's preamble (weight prefetch)

@@ -431,31 +431,10 @@ __global__ void __launch_bounds__(GM_THREADS) w4a16_gemm_tcgen05_kernel(const __
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * GM_BN) : "memory");
 }
 
-// Library-owned scratch for K-split launches, one per device: [counters, zero between launches][partial sums].
-// Allocated (counters zeroed) by the first call that needs it, grown when a larger problem arrives; at most one
+// Library-owned scratch for K-split launches: [counters, zero between launches][partial sums]; at most one
 // 256 x 256 fp32 tile per SM (37 MiB on 148 SMs).
 constexpr size_t GEMM_COUNTER_BYTES = 1024;
-static void *g_gemm_scratch[64] = {nullptr};
-static size_t g_gemm_scratch_bytes[64] = {0};
-static int gemm_scratch(size_t bytes, void **out) {
-  int dev = 0;
-  AB200_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
-  if (g_gemm_scratch_bytes[dev] < bytes) {
-    if (g_gemm_scratch[dev]) {
-      AB200_CUDA(cudaDeviceSynchronize());
-      AB200_CUDA(cudaFree(g_gemm_scratch[dev]));
-      g_gemm_scratch[dev] = nullptr;
-      g_gemm_scratch_bytes[dev] = 0;
-    }
-    AB200_CUDA(cudaMalloc(&g_gemm_scratch[dev], bytes));
-    AB200_CUDA(cudaMemset(g_gemm_scratch[dev], 0, GEMM_COUNTER_BYTES));
-    AB200_CUDA(cudaDeviceSynchronize());
-    g_gemm_scratch_bytes[dev] = bytes;
-  }
-  *out = g_gemm_scratch[dev];
-  return AB200_OK;
-}
+static int gemm_scratch(size_t bytes, void **out) { return library_buffer(LIB_BUF_GEMM, bytes, 0, GEMM_COUNTER_BYTES, out); }
 
 }  // namespace ab200
 

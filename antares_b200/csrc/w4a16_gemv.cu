@@ -568,30 +568,10 @@ static int gemv_f16_direct(GemvParams p, int M, cudaStream_t s) {
   return AB200_OK;
 }
 
-// Library-owned scratch for the persistent kernel's K-slice partials and tile counters: one
-// buffer per device, allocated (and zeroed) at the first call that needs it or needs more.
-static void *g_scratch[64] = {nullptr};
-static size_t g_scratch_bytes[64] = {0};
-
+// Library-owned scratch for the persistent kernel's K-slice partials and tile counters (all of it zeroed when allocated)
 static int library_scratch(size_t bytes, void **out) {
-  int dev = 0;
-  AB200_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
-  if (g_scratch_bytes[dev] < bytes) {
-    size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
-    if (g_scratch[dev]) {
-      AB200_CUDA(cudaDeviceSynchronize());
-      AB200_CUDA(cudaFree(g_scratch[dev]));
-      g_scratch[dev] = nullptr;
-      g_scratch_bytes[dev] = 0;
-    }
-    AB200_CUDA(cudaMalloc(&g_scratch[dev], want));
-    AB200_CUDA(cudaMemset(g_scratch[dev], 0, want));
-    AB200_CUDA(cudaDeviceSynchronize());
-    g_scratch_bytes[dev] = want;
-  }
-  *out = g_scratch[dev];
-  return AB200_OK;
+  const size_t want = bytes < ((size_t)8 << 20) ? ((size_t)8 << 20) : bytes;
+  return library_buffer(LIB_BUF_PERSIST, bytes, want, want, out);
 }
 
 template <int PRO>

@@ -380,27 +380,8 @@ typedef CUresult (*SlabEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Library-owned slab buffer, one per device (at most 43 stages x 9.2 KiB): allocated by the first call that needs it.
-static void *g_slabs[64] = {nullptr};
-static size_t g_slab_bytes[64] = {0};
-static int slab_scratch(size_t bytes, void **out) {
-  int dev = 0;
-  AB200_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
-  if (g_slab_bytes[dev] < bytes) {
-    if (g_slabs[dev]) {
-      AB200_CUDA(cudaDeviceSynchronize());
-      AB200_CUDA(cudaFree(g_slabs[dev]));
-      g_slabs[dev] = nullptr;
-      g_slab_bytes[dev] = 0;
-    }
-    const size_t want = bytes < ((size_t)1 << 20) ? ((size_t)1 << 20) : bytes;
-    AB200_CUDA(cudaMalloc(&g_slabs[dev], want));
-    g_slab_bytes[dev] = want;
-  }
-  *out = g_slabs[dev];
-  return AB200_OK;
-}
+// Library-owned slab buffer (at most 43 stages x 9.2 KiB for the 7B shapes): allocated by the first call that needs it.
+static int slab_scratch(size_t bytes, void **out) { return library_buffer(LIB_BUF_SLABS, bytes, (size_t)1 << 20, 0, out); }
 
 bool gemv_slab_eligible(int dtype, int M, int K, int N, int group) {
   return dtype == AB200_F16 && group == 128 && K % 128 == 0 && N % 8 == 0 && M >= 5 && M <= 16 && tensor_map_encoder() != nullptr;

@@ -659,29 +659,10 @@ typedef CUresult (*TcEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, v
                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Library-owned scratch, one per device: [counters, zero between launches][slabs][partials].  Allocated (and
-// zeroed) by the first call that needs it, grown when a larger problem arrives.
-static void *g_tc[64] = {nullptr};
-static size_t g_tc_bytes[64] = {0};
+// Library-owned scratch: [counters, zero between launches][slabs][partials]
 static int tc_scratch(size_t bytes, void **out) {
-  int dev = 0;
-  AB200_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(AB200_EUNSUPPORTED, "device index %d out of range", dev);
-  if (g_tc_bytes[dev] < bytes) {
-    if (g_tc[dev]) {
-      AB200_CUDA(cudaDeviceSynchronize());
-      AB200_CUDA(cudaFree(g_tc[dev]));
-      g_tc[dev] = nullptr;
-      g_tc_bytes[dev] = 0;
-    }
-    const size_t want = bytes < ((size_t)8 << 20) ? ((size_t)8 << 20) : bytes;
-    AB200_CUDA(cudaMalloc(&g_tc[dev], want));
-    AB200_CUDA(cudaMemset(g_tc[dev], 0, want));
-    AB200_CUDA(cudaDeviceSynchronize());
-    g_tc_bytes[dev] = want;
-  }
-  *out = g_tc[dev];
-  return AB200_OK;
+  const size_t want = bytes < ((size_t)8 << 20) ? ((size_t)8 << 20) : bytes;
+  return library_buffer(LIB_BUF_TC, bytes, want, want, out);
 }
 
 constexpr size_t TC_COUNTER_BYTES = 16 * 1024;  // up to 4096 column tiles
