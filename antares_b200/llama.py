@@ -291,16 +291,20 @@ class LlamaInt4Decoder:
         GEMM over all prompt tokens, attention is causal over the freshly written cache rows) instead
         of token by token as the reference does (samples/05_llama2_7b_int4.py:194-200).  Leaves the
         decoder exactly where token-by-token feeding would: cache rows 0..T-1 filled, pos = T,
-        token = the first generated token.  Returns that token (int).  Single GPU only."""
-        if self.world != 1:
-            raise NotImplementedError("batched prefill is implemented for one GPU (tensor-parallel runs feed the prompt through the decode step)")
+        token = the first generated token.  Returns that token (int).
+        Tensor parallel: the column-parallel projections are GEMMs on the rank's shard, the row-parallel ones
+        (O, down) produce fp16 partial sums that are added across ranks with one all-reduce each (on the
+        process group, i.e. NCCL), the classifier is vocabulary-parallel as in the decode step; the pass runs
+        eagerly (no graph) there."""
         cfg = self.cfg
         prompt = np.asarray(prompt, np.int32)
         T = int(len(prompt))
         assert 1 <= T <= cfg.max_seq and T <= self.max_tokens
         self.reset(torch.from_numpy(prompt).to(self.dev))
         cached = self._prefill_graphs.get(T)
-        if cached is None:
+        if self.world > 1:
+            self._prefill_pass(T, self._prefill_buffers(T))
+        elif cached is None:
             # first prompt of this length: run the pass eagerly, then record it as a CUDA graph over the same
             # buffers (352 launches at 32 layers: replayed, the pass is bound by the GPU, not by the host)
             bufs = self._prefill_buffers(T)
@@ -321,9 +325,9 @@ class LlamaInt4Decoder:
         return int(self.token.item())
 
     def _prefill_buffers(self, T):
-        d, f, dev = self.cfg.dim, self.fl, self.dev
+        d, dl, f, dev = self.cfg.dim, self.dl, self.fl, self.dev
         h16 = lambda *shape: torch.empty(*shape, dtype=torch.float16, device=dev)
-        return dict(x=torch.empty(T, d, dtype=torch.float32, device=dev), xb=h16(T, d), vqk=h16(T, 3 * d), q=h16(T, d), att=h16(T, d),
+        return dict(x=torch.empty(T, d, dtype=torch.float32, device=dev), xb=h16(T, d), vqk=h16(T, 3 * dl), q=h16(T, dl), att=h16(T, dl),
                     o=h16(T, d), gu=h16(T, 2 * f), hh=h16(T, f))
 
     def _prefill_pass(self, T, b):
@@ -347,19 +351,28 @@ class LlamaInt4Decoder:
             call("ab200_attention_prefill", q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), att.data_ptr(),
                  self.pos.data_ptr(), T, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
             gemm(att, l, "o", o)
+            if self.world > 1:
+                self.comm.all_reduce_sum_(o)
             call("ab200_residual_add_f16", x.data_ptr(), o.data_ptr(), T * d, st)
             call("ab200_rmsnorm", x.data_ptr(), 1, w["ffn_norm"].data_ptr(), xb.data_ptr(), T, d, cfg.eps, st)
             gemm(xb, l, "gu", gu)
             call("ab200_silu_mul_rows", gu.data_ptr(), hh.data_ptr(), T, f, st)
             gemm(hh, l, "down", o)
+            if self.world > 1:
+                self.comm.all_reduce_sum_(o)
             call("ab200_residual_add_f16", x.data_ptr(), o.data_ptr(), T * d, st)
         # classifier on the last token only, then the same bookkeeping as a decode step at pos = T - 1
         self.x.copy_(x[T - 1])
         self.pos.fill_(T - 1)
         call("ab200_rmsnorm", self.x.data_ptr(), 1, self.final_norm.data_ptr(), self.xb.data_ptr(), 1, d, cfg.eps, st)
         call("ab200_dense_gemv", self.xb.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(), d, self.vl, st)
-        call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), T, self.token.data_ptr(), self.pos.data_ptr(),
-             self.out_tokens.data_ptr(), self.out_tokens.numel(), st)
+        if self.world > 1 and hasattr(self.comm, "greedy_next_"):
+            self.comm.greedy_next_(self.logits_local, self.rank * self.vl, self.prompt, T, self.token, self.pos, self.out_tokens)
+        else:
+            if self.world > 1:
+                self.comm.all_gather_into(self.logits, self.logits_local)
+            call("ab200_greedy_next", self.logits.data_ptr(), cfg.vocab, self.prompt.data_ptr(), T, self.token.data_ptr(), self.pos.data_ptr(),
+                 self.out_tokens.data_ptr(), self.out_tokens.numel(), st)
         self.out_tokens[:T].copy_(toks)
 
     # -- graph ---------------------------------------------------------------------------------------
