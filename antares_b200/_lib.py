@@ -63,6 +63,9 @@ SIGNATURES = {
     "ab200_embed_lookup": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_rope_kv_store": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _vp],
     "ab200_attention_fused": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp],
+    "ab200_attention_fused_paged": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _l, _i, _f, _vp, _i, _vp],
+    "ab200_rope_kv_store_rows_paged": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _l, _i, _vp, _i, _vp],
+    "ab200_attention_prefill_paged": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _l, _f, _vp, _i, _vp],
     "ab200_silu_mul": [_vp, _vp, _i, _vp],
     "ab200_dense_gemv": [_vp, _vp, _vp, _i, _i, _vp],
     "ab200_hal_set_device": [_i],

@@ -41,7 +41,7 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *__restrict__ q, const T *__restrict__ kc,
                                                                       const T *__restrict__ vc, T *__restrict__ out,
                                                                       const int32_t *__restrict__ seq_len_dev, int seq_len_add,
-                                                                      int max_seq, long kv_stride, float scale) {
+                                                                      int max_seq, long kv_stride, float scale, KvPages pages) {
   extern __shared__ __align__(16) float att_smem[];
   float *p = att_smem;                // [max_seq]
   float *red = att_smem + max_seq;    // [16][128]
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *
     float dot = 0.f;
     if (s < S) {
       float kf[8];
-      ld8<T>(kh + (size_t)s * kv_stride, kf);
+      ld8<T>(kh + kv_row(pages, s) * kv_stride, kf);
 #pragma unroll
       for (int j = 0; j < 8; ++j) dot = fmaf(qf[j], kf[j], dot);
     }
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(const T *
   const T *vh = vc + (size_t)h * ATT_D + dchunk * 8;
   for (int s = sgroup; s < S; s += 16) {
     float vf[8];
-    ld8<T>(vh + (size_t)s * kv_stride, vf);
+    ld8<T>(vh + kv_row(pages, s) * kv_stride, vf);
     const float ps = p[s];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = fmaf(ps, vf[j], acc[j]);
@@ -136,6 +136,7 @@ struct AttnFusedParams {
   int H, max_seq;
   long kv_stride;
   float scale;
+  KvPages pages;
 };
 
 constexpr int ATT_PF = 4;  // cache rows per thread fetched before the current token's q/k/v exist
@@ -172,8 +173,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     const int s = split + i * splits;
     kreg[j] = vreg[j] = make_uint4(0, 0, 0, 0);
     if (i < n_local && s != pos) {
-      kreg[j] = ldg_stream_v4(kh + (size_t)s * p.kv_stride);
-      vreg[j] = ldg_stream_v4(vh + (size_t)s * p.kv_stride);
+      const size_t row = kv_row(p.pages, s);  // the page table, like the rows, dates from earlier steps
+      kreg[j] = ldg_stream_v4(kh + row * p.kv_stride);
+      vreg[j] = ldg_stream_v4(vh + row * p.kv_stride);
     }
   }
   float sn = 0.f, cs = 1.f;
@@ -197,8 +199,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
   __syncthreads();
   const bool own_new = (pos % splits) == split;
   if (own_new && threadIdx.x < ATT_D / 8) {
-    reinterpret_cast<uint4 *>(p.kc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(k_s)[threadIdx.x];
-    reinterpret_cast<uint4 *>(p.vc + (size_t)pos * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(v_s)[threadIdx.x];
+    const size_t row = kv_row(p.pages, pos);
+    reinterpret_cast<uint4 *>(p.kc + row * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(k_s)[threadIdx.x];
+    reinterpret_cast<uint4 *>(p.vc + row * p.kv_stride + (size_t)h * ATT_D)[threadIdx.x] = reinterpret_cast<const uint4 *>(v_s)[threadIdx.x];
   }
 
   // Each half-warp (16 lanes x 8 dims) runs an online softmax over its rows i = sgroup + 16 * pass:
@@ -242,8 +245,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_fused_kernel(AttnFusedP
     const bool live = i < n_local, cur = (s == pos);
     uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
     if (live) {
-      kv = cur ? reinterpret_cast<const uint4 *>(k_s)[chunk] : ldg_stream_v4(kh + (size_t)s * p.kv_stride);
-      vv = cur ? reinterpret_cast<const uint4 *>(v_s)[chunk] : ldg_stream_v4(vh + (size_t)s * p.kv_stride);
+      const size_t row = cur ? 0 : kv_row(p.pages, s);
+      kv = cur ? reinterpret_cast<const uint4 *>(k_s)[chunk] : ldg_stream_v4(kh + row * p.kv_stride);
+      vv = cur ? reinterpret_cast<const uint4 *>(v_s)[chunk] : ldg_stream_v4(vh + row * p.kv_stride);
     }
     row_step(live, kv, vv);
   }
@@ -355,13 +359,13 @@ extern "C" int ab200_attention_decode(const void *q_f16, const void *k_cache_f16
       AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attention_decode_kernel<__half><<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const __half *)q_f16, (const __half *)k_cache_f16,
                                                                                    (const __half *)v_cache_f16, (__half *)out_f16, seq_len_dev,
-                                                                                   seq_len_add, max_seq, kv_stride, scale);
+                                                                                   seq_len_add, max_seq, kv_stride, scale, KvPages{nullptr, 0});
   } else if (dtype == AB200_F32) {
     if (smem > 48 * 1024)
       AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attention_decode_kernel<float><<<H, ATT_THREADS, smem, (cudaStream_t)stream>>>((const float *)q_f16, (const float *)k_cache_f16,
                                                                                   (const float *)v_cache_f16, (float *)out_f16, seq_len_dev,
-                                                                                  seq_len_add, max_seq, kv_stride, scale);
+                                                                                  seq_len_add, max_seq, kv_stride, scale, KvPages{nullptr, 0});
   } else {
     return fail(AB200_EINVAL, "attention_decode: unknown dtype %d", dtype);
   }
@@ -381,10 +385,18 @@ extern "C" int ab200_dense_gemv(const void *x_f16, const void *w_f16, float *log
   return AB200_OK;
 }
 
-extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev, void *k_cache_f16,
-                                     void *v_cache_f16, void *out_f16, int H, int D, long kv_stride, int max_seq, float scale,
-                                     void *stream) {
+// page_rows: 0 = contiguous cache, else a power of two (rows per page) with page_table[(max_seq + page_rows - 1) / page_rows]
+static int page_shift_of(int page_rows) {
+  int shift = 0;
+  while ((1 << shift) < page_rows) ++shift;
+  return (page_rows > 0 && (1 << shift) == page_rows) ? shift : -1;
+}
+
+static int attention_fused_impl(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev, void *k_cache_f16,
+                                void *v_cache_f16, void *out_f16, int H, int D, long kv_stride, int max_seq, float scale,
+                                const int32_t *page_table, int page_rows, void *stream) {
   clear_error();
+  AB200_REQUIRE(page_table == nullptr || page_shift_of(page_rows) >= 0, "attention_fused: page_rows=%d must be a power of two", page_rows);
   AB200_REQUIRE(vqk_f16 && inv_freq && pos_dev && k_cache_f16 && v_cache_f16 && out_f16, "attention_fused: null pointer");
   AB200_REQUIRE(D == ATT_D, "attention_fused: head size %d is not the built size %d", D, ATT_D);
   AB200_REQUIRE(H > 0 && max_seq > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0, "attention_fused: bad shape H=%d max_seq=%d kv_stride=%ld", H, max_seq, kv_stride);
@@ -393,7 +405,7 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   int splits = 1;
   while (splits < 8 && H * splits * 2 <= 2 * sm_count()) splits *= 2;  // up to ~2 CTAs per SM, at most 8 per head
   AttnFusedParams p{(const __half *)vqk_f16, inv_freq, pos_dev, (__half *)k_cache_f16, (__half *)v_cache_f16, (__half *)out_f16,
-                    H, max_seq, kv_stride, scale};
+                    H, max_seq, kv_stride, scale, KvPages{page_table, page_table ? page_shift_of(page_rows) : 0}};
   const size_t smem = ((size_t)16 * ATT_D + ATT_D + 2 * 8) * sizeof(float);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(H * splits, 1, 1);
@@ -413,12 +425,27 @@ extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq,
   return AB200_OK;
 }
 
+extern "C" int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev, void *k_cache_f16,
+                                     void *v_cache_f16, void *out_f16, int H, int D, long kv_stride, int max_seq, float scale,
+                                     void *stream) {
+  return attention_fused_impl(vqk_f16, inv_freq, pos_dev, k_cache_f16, v_cache_f16, out_f16, H, D, kv_stride, max_seq, scale, nullptr, 0, stream);
+}
+
+extern "C" int ab200_attention_fused_paged(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev, void *k_cache_f16,
+                                           void *v_cache_f16, void *out_f16, int H, int D, long kv_stride, int max_seq, float scale,
+                                           const int32_t *page_table, int page_rows, void *stream) {
+  if (!page_table) return fail(AB200_EINVAL, "attention_fused_paged: null page table");
+  return attention_fused_impl(vqk_f16, inv_freq, pos_dev, k_cache_f16, v_cache_f16, out_f16, H, D, kv_stride, max_seq, scale, page_table, page_rows, stream);
+}
+
 // Causal attention of `rows` consecutive tokens over a cache that already holds their keys and
 // values: query row r (position *pos0_dev + r) attends cache rows 0 .. *pos0_dev + r.  The batched
 // form of ab200_attention_decode (grid = heads x rows).
-extern "C" int ab200_attention_prefill(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16, const int32_t *pos0_dev,
-                                       int rows, int max_seq, int H, int D, long kv_stride, float scale, void *stream) {
+static int attention_prefill_impl(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16, const int32_t *pos0_dev,
+                                  int rows, int max_seq, int H, int D, long kv_stride, float scale, const int32_t *page_table, int page_rows,
+                                  void *stream) {
   clear_error();
+  AB200_REQUIRE(page_table == nullptr || page_shift_of(page_rows) >= 0, "attention_prefill: page_rows=%d must be a power of two", page_rows);
   AB200_REQUIRE(q_f16 && k_cache_f16 && v_cache_f16 && out_f16 && pos0_dev && rows > 0 && rows <= 65535, "attention_prefill: bad argument");
   AB200_REQUIRE(D == ATT_D, "attention_prefill: head size %d is not the built size %d", D, ATT_D);
   AB200_REQUIRE(H > 0 && max_seq > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0, "attention_prefill: bad shape H=%d max_seq=%d kv_stride=%ld", H, max_seq, kv_stride);
@@ -427,7 +454,20 @@ extern "C" int ab200_attention_prefill(const void *q_f16, const void *k_cache_f1
   if (smem > 200 * 1024) return fail(AB200_EUNSUPPORTED, "attention_prefill: max_seq=%d exceeds the shared-memory score buffer", max_seq);
   if (smem > 48 * 1024) AB200_CUDA(cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   attention_decode_kernel<__half><<<dim3(H, rows), ATT_THREADS, smem, (cudaStream_t)stream>>>(
-      (const __half *)q_f16, (const __half *)k_cache_f16, (const __half *)v_cache_f16, (__half *)out_f16, pos0_dev, 1, max_seq, kv_stride, scale);
+      (const __half *)q_f16, (const __half *)k_cache_f16, (const __half *)v_cache_f16, (__half *)out_f16, pos0_dev, 1, max_seq, kv_stride, scale,
+      KvPages{page_table, page_table ? page_shift_of(page_rows) : 0});
   AB200_CHECK_LAUNCH("attention_prefill");
   return AB200_OK;
+}
+
+extern "C" int ab200_attention_prefill(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16, const int32_t *pos0_dev,
+                                       int rows, int max_seq, int H, int D, long kv_stride, float scale, void *stream) {
+  return attention_prefill_impl(q_f16, k_cache_f16, v_cache_f16, out_f16, pos0_dev, rows, max_seq, H, D, kv_stride, scale, nullptr, 0, stream);
+}
+
+extern "C" int ab200_attention_prefill_paged(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16, void *out_f16,
+                                             const int32_t *pos0_dev, int rows, int max_seq, int H, int D, long kv_stride, float scale,
+                                             const int32_t *page_table, int page_rows, void *stream) {
+  if (!page_table) return fail(AB200_EINVAL, "attention_prefill_paged: null page table");
+  return attention_prefill_impl(q_f16, k_cache_f16, v_cache_f16, out_f16, pos0_dev, rows, max_seq, H, D, kv_stride, scale, page_table, page_rows, stream);
 }

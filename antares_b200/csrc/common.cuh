@@ -69,6 +69,16 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// Paged KV cache: logical cache row s lives in physical row table[s >> shift] * 2^shift + (s mod 2^shift);
+// table == nullptr means the cache is contiguous (physical row = s).
+struct KvPages {
+  const int32_t *table;
+  int shift;
+};
+__device__ __forceinline__ size_t kv_row(const KvPages &pg, int s) {
+  return pg.table ? ((size_t)pg.table[s >> pg.shift] << pg.shift) + (size_t)(s & ((1 << pg.shift) - 1)) : (size_t)s;
+}
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -273,14 +273,15 @@ __global__ void embed_lookup_kernel(const __half *__restrict__ embed, const int3
 __global__ void __launch_bounds__(ROW_THREADS) rope_kv_store_kernel(const __half *__restrict__ vqk, const float *__restrict__ inv_freq,
                                                                    const int32_t *__restrict__ pos_dev, __half *__restrict__ q_out,
                                                                    __half *__restrict__ kc, __half *__restrict__ vc, int H, int D,
-                                                                   long kv_stride, int max_seq) {
+                                                                   long kv_stride, int max_seq, KvPages pages) {
   const int pos = *pos_dev + (int)blockIdx.x;  // one token per block: positions pos, pos + 1, ...
   if (pos < 0 || pos >= max_seq) return;  // out-of-range step: leave the cache untouched
   const int HD = H * D, half = D / 2, chunks = half / 8;
   vqk += (size_t)blockIdx.x * 3 * HD;
   q_out += (size_t)blockIdx.x * HD;
   const __half *v = vqk, *q = vqk + HD, *k = vqk + 2 * HD;
-  __half *krow = kc + (size_t)pos * kv_stride, *vrow = vc + (size_t)pos * kv_stride;
+  const size_t prow = kv_row(pages, pos);
+  __half *krow = kc + prow * kv_stride, *vrow = vc + prow * kv_stride;
   for (int i = threadIdx.x; i < HD / 8; i += ROW_THREADS)
     *reinterpret_cast<uint4 *>(vrow + (size_t)i * 8) = *reinterpret_cast<const uint4 *>(v + (size_t)i * 8);
   const int jc = threadIdx.x % chunks, hslot = threadIdx.x / chunks, hstep = ROW_THREADS / chunks;
@@ -510,7 +511,7 @@ extern "C" int ab200_rope_kv_store(const void *vqk_f16, const float *inv_freq, c
   AB200_REQUIRE(aligned16(vqk_f16) && aligned16(q_out_f16) && aligned16(k_cache_f16) && aligned16(v_cache_f16),
                 "rope_kv_store: pointers must be 16-byte aligned");
   rope_kv_store_kernel<<<1, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)vqk_f16, inv_freq, pos_dev, (__half *)q_out_f16,
-                                                                  (__half *)k_cache_f16, (__half *)v_cache_f16, H, D, kv_stride, max_seq);
+                                                                  (__half *)k_cache_f16, (__half *)v_cache_f16, H, D, kv_stride, max_seq, KvPages{nullptr, 0});
   AB200_CHECK_LAUNCH("rope_kv_store");
   return AB200_OK;
 }
@@ -535,18 +536,38 @@ extern "C" int ab200_embed_rows(const void *embed_f16, const int32_t *tokens_dev
   return AB200_OK;
 }
 
-extern "C" int ab200_rope_kv_store_rows(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev, void *q_out_f16, void *k_cache_f16,
-                                        void *v_cache_f16, int rows, int H, int D, long kv_stride, int max_seq, void *stream) {
+static int rope_kv_store_rows_impl(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev, void *q_out_f16, void *k_cache_f16,
+                                   void *v_cache_f16, int rows, int H, int D, long kv_stride, int max_seq, const int32_t *page_table,
+                                   int page_rows, void *stream) {
   clear_error();
   AB200_REQUIRE(vqk_f16 && inv_freq && pos0_dev && q_out_f16 && k_cache_f16 && v_cache_f16 && rows > 0, "rope_kv_store_rows: bad argument");
   AB200_REQUIRE(D > 0 && D % 16 == 0 && D / 16 <= ROW_THREADS && H > 0 && kv_stride >= (long)H * D && kv_stride % 8 == 0,
                 "rope_kv_store_rows: bad shape H=%d D=%d kv_stride=%ld", H, D, kv_stride);
   AB200_REQUIRE(aligned16(vqk_f16) && aligned16(q_out_f16) && aligned16(k_cache_f16) && aligned16(v_cache_f16),
                 "rope_kv_store_rows: pointers must be 16-byte aligned");
+  int shift = 0;
+  if (page_table) {
+    while ((1 << shift) < page_rows) ++shift;
+    AB200_REQUIRE(page_rows > 0 && (1 << shift) == page_rows, "rope_kv_store_rows: page_rows=%d must be a power of two", page_rows);
+  }
   rope_kv_store_kernel<<<rows, ROW_THREADS, 0, (cudaStream_t)stream>>>((const __half *)vqk_f16, inv_freq, pos0_dev, (__half *)q_out_f16,
-                                                                     (__half *)k_cache_f16, (__half *)v_cache_f16, H, D, kv_stride, max_seq);
+                                                                     (__half *)k_cache_f16, (__half *)v_cache_f16, H, D, kv_stride, max_seq,
+                                                                     KvPages{page_table, shift});
   AB200_CHECK_LAUNCH("rope_kv_store_rows");
   return AB200_OK;
+}
+
+extern "C" int ab200_rope_kv_store_rows(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev, void *q_out_f16, void *k_cache_f16,
+                                        void *v_cache_f16, int rows, int H, int D, long kv_stride, int max_seq, void *stream) {
+  return rope_kv_store_rows_impl(vqk_f16, inv_freq, pos0_dev, q_out_f16, k_cache_f16, v_cache_f16, rows, H, D, kv_stride, max_seq, nullptr, 0, stream);
+}
+
+extern "C" int ab200_rope_kv_store_rows_paged(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev, void *q_out_f16,
+                                              void *k_cache_f16, void *v_cache_f16, int rows, int H, int D, long kv_stride, int max_seq,
+                                              const int32_t *page_table, int page_rows, void *stream) {
+  if (!page_table) return fail(AB200_EINVAL, "rope_kv_store_rows_paged: null page table");
+  return rope_kv_store_rows_impl(vqk_f16, inv_freq, pos0_dev, q_out_f16, k_cache_f16, v_cache_f16, rows, H, D, kv_stride, max_seq, page_table, page_rows,
+                                 stream);
 }
 
 extern "C" int ab200_silu_mul_rows(const void *gate_up_f16, void *out_f16, int rows, int n, void *stream) {

@@ -143,7 +143,7 @@ class LlamaInt4Decoder:
     """
 
     def __init__(self, cfg, device, rank=0, world=1, comm=None, max_tokens=1024, prefetch=0, weights=None, tiled=True,
-                 fused_allreduce=True):
+                 fused_allreduce=True, kv_page_rows=0, kv_page_table=None):
         assert cfg.dim % (world * cfg.group) == 0 and cfg.n_heads % world == 0 and cfg.vocab % world == 0
         self.cfg, self.dev, self.rank, self.world, self.comm = cfg, device, rank, world, comm
         self.hl = cfg.n_heads // world            # local heads
@@ -167,8 +167,19 @@ class LlamaInt4Decoder:
         self.final_norm = t(gl["final_norm"])
         self.inv_freq = t(make_inv_freq(cfg.head_dim, cfg.rope_base))
         z = lambda *s, dt=torch.float16: torch.zeros(*s, dtype=dt, device=device)
-        self.k_cache = z(cfg.n_layers, cfg.max_seq, self.dl)
-        self.v_cache = z(cfg.n_layers, cfg.max_seq, self.dl)
+        # KV cache: contiguous [layer, max_seq, dl], or paged: kv_page_rows (a power of two) rows per page and a
+        # table logical page -> physical page (identity unless kv_page_table is given; the same table for every layer)
+        self.kv_page_rows = int(kv_page_rows)
+        self.page_table = None
+        phys_rows = cfg.max_seq
+        if self.kv_page_rows:
+            n_pages = (cfg.max_seq + self.kv_page_rows - 1) // self.kv_page_rows
+            table = np.arange(n_pages, dtype=np.int32) if kv_page_table is None else np.asarray(kv_page_table, np.int32)
+            assert table.shape == (n_pages,) and sorted(table.tolist()) == list(range(n_pages)), "kv_page_table must be a permutation of the pages"
+            self.page_table = torch.from_numpy(table).to(device)
+            phys_rows = n_pages * self.kv_page_rows
+        self.k_cache = z(cfg.n_layers, phys_rows, self.dl)
+        self.v_cache = z(cfg.n_layers, phys_rows, self.dl)
         self.x = z(cfg.dim, dt=torch.float32)
         self.xb = z(cfg.dim)
         self.vqk = z(3 * self.dl)
@@ -251,9 +262,14 @@ class LlamaInt4Decoder:
         self._n += 1
         for l, w in enumerate(self.layers):
             self._proj(self.x, w["vqk_q"], w["vqk_s"], self.vqk, 1, 0, w["att_norm"])        # RMSNorm + V|Q|K
-            call("ab200_attention_fused", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(),
-                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.att.data_ptr(), self.hl, cfg.head_dim,
-                 self.dl, cfg.max_seq, self.att_scale, st)                                  # RoPE + cache + attention
+            if self.page_table is None:
+                call("ab200_attention_fused", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(),
+                     self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.att.data_ptr(), self.hl, cfg.head_dim,
+                     self.dl, cfg.max_seq, self.att_scale, st)                              # RoPE + cache + attention
+            else:
+                call("ab200_attention_fused_paged", self.vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(),
+                     self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), self.att.data_ptr(), self.hl, cfg.head_dim,
+                     self.dl, cfg.max_seq, self.att_scale, self.page_table.data_ptr(), self.kv_page_rows, st)
             self._n += 1
             self._row_parallel(self.att, w["o_q"], w["o_s"], 0)                               # O + residual
             self._proj(self.x, w["gu_q"], w["gu_s"], self.gu, 1, 0, w["ffn_norm"])           # RMSNorm + gate|up
@@ -346,10 +362,17 @@ class LlamaInt4Decoder:
         for l, w in enumerate(self.layers):
             call("ab200_rmsnorm", x.data_ptr(), 1, w["att_norm"].data_ptr(), xb.data_ptr(), T, d, cfg.eps, st)
             gemm(xb, l, "vqk", vqk)
-            call("ab200_rope_kv_store_rows", vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), q.data_ptr(),
-                 self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), T, self.hl, cfg.head_dim, self.dl, cfg.max_seq, st)
-            call("ab200_attention_prefill", q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), att.data_ptr(),
-                 self.pos.data_ptr(), T, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
+            if self.page_table is None:
+                call("ab200_rope_kv_store_rows", vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), q.data_ptr(),
+                     self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), T, self.hl, cfg.head_dim, self.dl, cfg.max_seq, st)
+                call("ab200_attention_prefill", q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), att.data_ptr(),
+                     self.pos.data_ptr(), T, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, st)
+            else:
+                pt, pr = self.page_table.data_ptr(), self.kv_page_rows
+                call("ab200_rope_kv_store_rows_paged", vqk.data_ptr(), self.inv_freq.data_ptr(), self.pos.data_ptr(), q.data_ptr(),
+                     self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), T, self.hl, cfg.head_dim, self.dl, cfg.max_seq, pt, pr, st)
+                call("ab200_attention_prefill_paged", q.data_ptr(), self.k_cache[l].data_ptr(), self.v_cache[l].data_ptr(), att.data_ptr(),
+                     self.pos.data_ptr(), T, cfg.max_seq, self.hl, cfg.head_dim, self.dl, self.att_scale, pt, pr, st)
             gemm(att, l, "o", o)
             if self.world > 1:
                 self.comm.all_reduce_sum_(o)

@@ -488,7 +488,8 @@ def run_ours(args):
         _ops.set_option("pdl", args.pdl)
     cfg = LlamaConfig(max_seq=max(N_PROMPT + W + K + 8, 168))
     dec = LlamaInt4Decoder(cfg, dev, rank=rank, world=world, comm=comm, max_tokens=max(N_PROMPT + W + K + 8, 168),
-                           prefetch=args.prefetch, tiled=not args.reference_layout, fused_allreduce=not args.separate_allreduce)
+                           prefetch=args.prefetch, tiled=not args.reference_layout, fused_allreduce=not args.separate_allreduce,
+                           kv_page_rows=args.kv_page_rows)
     prompt = synth_prompt(cfg, N_PROMPT, 0)
     dec.prompt[:N_PROMPT].copy_(torch.from_numpy(prompt))
     dec.capture(N_PROMPT)
@@ -600,7 +601,8 @@ def run_ours(args):
                        "parallelism": "tp%d" % world,
                        "allreduce": ("none" if world == 1 else ("nccl" if args.comm == "nccl" else ("push, fused into the O/down projections" if dec.fused_allreduce else "push, separate kernel"))), "l2": "each step streams %.2f GB of weights per GPU (> L2), no flush needed" % (step_bytes / 1e9),
                        "launcher": "cuda graph, 1 replay per token",
-                       "weight_layout": "reference [K/8, N]" if args.reference_layout else "tile-major [N/128][K/8][128] (repacked at load)"},
+                       "weight_layout": "reference [K/8, N]" if args.reference_layout else "tile-major [N/128][K/8][128] (repacked at load)",
+                       "kv_cache": ("paged, %d rows per page" % args.kv_page_rows) if args.kv_page_rows else "contiguous"},
             "e2e": {"value": K / sec_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": dec.launches_per_step * K, "launches_per_step": dec.launches_per_step,
             "clocks": clocks, "roofline": roof,
@@ -652,6 +654,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--repeats", type=int, default=REPEATS, help="how many times the K-step timed region is repeated (median reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-page-rows", type=int, default=0, help="KV cache in pages of this many rows (a power of two) behind a page table; 0 = contiguous (the default, as in the reference)")
     ap.add_argument("--no-extras", action="store_true", help="skip the operator-level figures (prefill GEMM, GEMV set)")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 release dependents at kernel start, 2 after the GEMV streaming loop")
     ap.add_argument("--reference-layout", action="store_true", help="keep the weights in the reference's [K/8, N] layout instead of tile-major")

@@ -229,6 +229,26 @@ int ab200_attention_fused(const void *vqk_f16, const float *inv_freq, const int3
                           void *k_cache_f16, void *v_cache_f16, void *out_f16, int H, int D,
                           long kv_stride, int max_seq, float scale, void *stream);
 
+/* Paged KV cache (the reference keeps one contiguous [seq_len, 4096] cache per layer,
+ * samples/05_llama2_7b_int4.py:119-120; a serving host hands out cache rows in pages).  The _paged
+ * forms of the three calls that touch the cache take a device table int32[ceil(max_seq /
+ * page_rows)], page_rows a power of two: logical cache row s lives in physical row
+ * page_table[s / page_rows] * page_rows + s % page_rows of k_cache / v_cache.  max_seq stays the
+ * logical length.  The table entries of rows at or below the current position must be in place
+ * before the call (the fused decode form reads them before the preceding kernel has finished). */
+int ab200_attention_fused_paged(const void *vqk_f16, const float *inv_freq, const int32_t *pos_dev,
+                                void *k_cache_f16, void *v_cache_f16, void *out_f16, int H, int D,
+                                long kv_stride, int max_seq, float scale, const int32_t *page_table,
+                                int page_rows, void *stream);
+int ab200_rope_kv_store_rows_paged(const void *vqk_f16, const float *inv_freq, const int32_t *pos0_dev,
+                                   void *q_out_f16, void *k_cache_f16, void *v_cache_f16, int rows,
+                                   int H, int D, long kv_stride, int max_seq,
+                                   const int32_t *page_table, int page_rows, void *stream);
+int ab200_attention_prefill_paged(const void *q_f16, const void *k_cache_f16, const void *v_cache_f16,
+                                  void *out_f16, const int32_t *pos0_dev, int rows, int max_seq, int H,
+                                  int D, long kv_stride, float scale, const int32_t *page_table,
+                                  int page_rows, void *stream);
+
 /* out[i] = silu(gate_up[i]) * gate_up[n + i], fp32 math (line 171). */
 int ab200_silu_mul(const void *gate_up_f16, void *out_f16, int n, void *stream);
 

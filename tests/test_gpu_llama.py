@@ -103,6 +103,27 @@ def test_batched_prefill_matches_token_by_token(cuda):
     assert ops.kernel_status() == 0
 
 
+def test_paged_kv_cache_is_bitwise_the_contiguous_one(cuda):
+    """A cache handed out in pages of 16 rows through a shuffled page table gives bit-identical logits and tokens,
+    token by token and through the batched prompt pass, and its rows are the contiguous cache's rows, permuted."""
+    cfg = LlamaConfig(n_layers=2, max_seq=96)
+    prompt = synth_prompt(cfg, 37, 11)
+    rows = 16
+    table = np.random.default_rng(5).permutation(cfg.max_seq // rows).astype(np.int32)
+    for batched in (False, True):
+        flat = LlamaInt4Decoder(cfg, cuda)
+        paged = LlamaInt4Decoder(cfg, cuda, kv_page_rows=rows, kv_page_table=table)
+        want = flat.generate(prompt, 9, batched_prefill=batched)
+        got = paged.generate(prompt, 9, batched_prefill=batched)
+        assert list(got) == list(want)
+        assert torch.equal(paged.logits, flat.logits)
+        n = len(prompt) + 8                                # cache rows written: positions 0 .. n - 1
+        s = torch.arange(n, device=cuda)
+        phys = torch.from_numpy(table).to(cuda)[s // rows].long() * rows + s % rows
+        assert torch.equal(paged.k_cache[:, phys], flat.k_cache[:, :n]) and torch.equal(paged.v_cache[:, phys], flat.v_cache[:, :n])
+    assert ops.kernel_status() == 0
+
+
 def _teacher_forced_logits(dec, tokens, positions, cuda):
     """Feeds `tokens` one by one through the host-token API and returns {position: logits} for the
     requested positions (logits after the token at that position went in)."""
