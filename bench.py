@@ -591,6 +591,28 @@ def run_ours(args):
     peak, peak_kind = measured_peaks()
     roof = gemv_roofline(dec, torch, peak, peak_kind)
     step_bytes = statistics.mean(dec.step_bytes(p) for p in range(N_PROMPT + W, N_PROMPT + W + K))
+    # time to first token for the 128-token prompt: the reference's way (token by token through
+    # the decode step) and the batched prefill (tensor-core GEMMs over all prompt tokens); every rank takes part
+    ttft = None
+    if not args.no_extras:
+        ttft = {}
+        for name in ("token_by_token", "batched_prefill"):
+            best = None
+            for _ in range(3):
+                fence()
+                t0 = time.perf_counter()
+                if name == "batched_prefill":
+                    dec.prefill(prompt)
+                else:
+                    dec.reset(torch.from_numpy(prompt).to(dev))
+                    for _ in range(N_PROMPT):
+                        dec.graph.replay()
+                fence()
+                dt = (time.perf_counter() - t0) * 1e3
+                best = dt if best is None else min(best, dt)
+            ttft[name + "_ms"] = best
+            ttft[name + "_first_token"] = int(dec.token.item())
+        check_status("the time-to-first-token runs")
     if rank != 0:
         return None
     line = {"metric": METRIC, "value": K / sec, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -618,29 +640,12 @@ def run_ours(args):
         if os.path.exists(path):
             with open(path) as f:
                 tensor_peak = float(json.load(f).get("bf16_tflops", tensor_peak))
-        # time to first token for the 128-token prompt: the reference's way (token by token through
-        # the decode step) and the batched prefill (tensor-core GEMMs over all prompt tokens)
-        ttft = {}
-        for name in ("token_by_token", "batched_prefill"):
-            best = None
-            for _ in range(3):
-                fence()
-                t0 = time.perf_counter()
-                if name == "batched_prefill":
-                    dec.prefill(prompt)
-                else:
-                    dec.reset(torch.from_numpy(prompt).to(dev))
-                    for _ in range(N_PROMPT):
-                        dec.graph.replay()
-                fence()
-                dt = (time.perf_counter() - t0) * 1e3
-                best = dt if best is None else min(best, dt)
-            ttft[name + "_ms"] = best
-            ttft[name + "_first_token"] = int(dec.token.item())
         del dec
         torch.cuda.empty_cache()
         line["extras"] = extras_single_ops(torch, dev, peak, tensor_peak)
         line["extras"]["time_to_first_token_128"] = ttft
+    elif ttft is not None:
+        line["extras"] = {"time_to_first_token_128": ttft}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = run_reference(argparse.Namespace(steps=20, warmup=0, gpus=1), as_baseline=True)
     return line
