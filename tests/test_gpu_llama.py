@@ -124,6 +124,21 @@ def test_paged_kv_cache_is_bitwise_the_contiguous_one(cuda):
     assert ops.kernel_status() == 0
 
 
+def test_paged_calls_reject_bad_page_tables(cuda):
+    from antares_b200 import _lib
+    cfg = LlamaConfig(n_layers=1, max_seq=64)
+    dec = LlamaInt4Decoder(cfg, cuda, kv_page_rows=16)
+    st = torch.cuda.current_stream().cuda_stream
+    args = (dec.vqk.data_ptr(), dec.inv_freq.data_ptr(), dec.pos.data_ptr(), dec.k_cache[0].data_ptr(), dec.v_cache[0].data_ptr(),
+            dec.att.data_ptr(), dec.hl, cfg.head_dim, dec.dl, cfg.max_seq, dec.att_scale)
+    with pytest.raises(_lib.Ab200Error):
+        _lib.call("ab200_attention_fused_paged", *args, dec.page_table.data_ptr(), 12, st)   # not a power of two
+    with pytest.raises(_lib.Ab200Error):
+        _lib.call("ab200_attention_fused_paged", *args, 0, 16, st)                           # no table
+    with pytest.raises(AssertionError):
+        LlamaInt4Decoder(cfg, cuda, kv_page_rows=16, kv_page_table=[0, 0, 1, 2])              # not a permutation
+
+
 def _teacher_forced_logits(dec, tokens, positions, cuda):
     """Feeds `tokens` one by one through the host-token API and returns {position: logits} for the
     requested positions (logits after the token at that position went in)."""
