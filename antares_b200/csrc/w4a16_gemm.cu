@@ -28,6 +28,11 @@
 // through mbarriers (weights ready, x tile landed, MMAs done), there is no block-wide barrier inside the
 // K loop.  The epilogue reads the accumulators with `tcgen05.ld` (row = TMEM lane; the four warps that
 // share a lane quarter split the 512 columns), rounds to fp16 and stores.
+// Short prompts: an accumulator whose 128 rows all lie beyond M is left out (its issuing thread only keeps
+// the barriers in step), and when the problem has fewer tiles than half the SMs the grid's z dimension
+// splits K into up to four ranges: every CTA stores its fp32 accumulators as partial sums (laid out so
+// that a warp's 32 rows of 16 columns are consecutive), the last CTA of a tile to arrive adds the parts in
+// part order - bitwise repeatable - and runs the epilogue.
 // Every mbarrier wait is bounded and reports through the status word.
 #include <cuda.h>  // CUtensorMap and its enums (types only)
 
