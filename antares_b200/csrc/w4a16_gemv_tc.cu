@@ -31,11 +31,13 @@
 // Every wait is bounded (status sites 600-680).
 //
 // Measured on B200 (gate|up projection 4096 x 22016, isolated, cold weights): 24 us at 1 row, 30 us at 16,
-// against 11 us (scalar kernel, 1 row) and 20 us (warp-MMA ring kernel, 16 rows).  Device timestamps show the
-// two MMA-issuing threads as the limit: an M128 N16 K16 instruction costs its issuing thread about 100 cycles
-// and a 256-k stage needs 16 of them (about 1800 cycles per stage and CTA, 9 stages per CTA), and the
-// exchange of partial sums adds 3-5 us at the end.  The instruction count does not depend on N, so the
-// same structure would pay off only at batch sizes well beyond 16.
+// against 11 us (scalar kernel, 1 row) and 20 us (warp-MMA ring kernel, 16 rows).  Device timestamps put the
+// main loop at about 1800 cycles per 256-k stage and CTA (bounded by the two MMA-issuing threads: an M128 N16
+// K16 instruction costs its issuing thread about 100 cycles and a stage needs 16 of them), 9 stages per CTA:
+// 8.5 us, close to the 7.1 us the bytes take at the measured HBM rate.  The rest is what surrounds the loop: the
+// activation kernel in front (launch + run, serialised by the dependency), ring ramp-up behind the TMEM
+// allocation, and the exchange of partial sums (3-5 us at 16 rows).  The instruction count does not depend on
+// N, so the same structure would pay off at batch sizes well beyond 16.
 #include <cuda.h>  // CUtensorMap (types only)
 
 #include "common.cuh"
