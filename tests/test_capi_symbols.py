@@ -26,6 +26,20 @@ def test_python_binding_covers_the_header():
     assert sorted(list(_lib.SIGNATURES) + _lib.OTHER_SYMBOLS) == _declared()
 
 
+def test_python_signatures_have_the_headers_argument_counts():
+    """A ctypes signature with one argument too few or too many corrupts the call silently: every entry of
+    _lib.SIGNATURES must list as many arguments as the header's declaration of that function."""
+    text = open(os.path.join(ROOT, "include", "antares_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    counts = {}
+    for name, params in re.findall(r"\b(ab200_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        params = params.strip()
+        counts[name] = 0 if params in ("", "void") else params.count(",") + 1
+    for name, sig in _lib.SIGNATURES.items():
+        assert name in counts, name
+        assert len(sig) == counts[name], "%s: header declares %d arguments, the binding passes %d" % (name, counts[name], len(sig))
+
+
 def test_abi_version_and_error_text_without_gpu():
     L = _lib.load()
     assert L.ab200_abi_version() == 1
